@@ -1,0 +1,61 @@
+// Small elementwise kernels: SiLU(gate) * up on the fused gate|up projection,
+// and conversions between 32-bit and bfloat16.
+#include "common.cuh"
+
+// in [n_rows, 2 I] with the gate in columns [0, I) and up in [I, 2 I);
+// out[r, i] = g / (1 + exp(-g)) * u in 32-bit, one rounding at the store
+// (the reference's silu_mul_2d_f16, src/kernels.rs:271-296).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int I) {
+  const size_t r = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= I) return;
+  const float g = to_f32<T>(in[r * 2 * I + i]);
+  const float u = to_f32<T>(in[r * 2 * I + I + i]);
+  out[r * I + i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+
+template <typename T>
+static int silu_mul(const void* in, void* out, int n_rows, int I, cudaStream_t s) {
+  if (n_rows < 0 || I <= 0) return GB_ERR_BAD_ARG;
+  if (n_rows == 0) return 0;
+  if (n_rows > 65535) {
+    // rows go to grid.y; split very long steps
+    for (int r0 = 0; r0 < n_rows; r0 += 65535) {
+      const int n = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
+      int e = silu_mul<T>((const T*)in + (size_t)r0 * 2 * I, (T*)out + (size_t)r0 * I, n, I, s);
+      if (e) return e;
+    }
+    return 0;
+  }
+  silu_mul_kernel<T><<<dim3((I + 255) / 256, n_rows), 256, 0, s>>>((const T*)in, (T*)out, I);
+  return gb_status();
+}
+GB_EXPORT int gb_silu_mul_f32(const void* in, void* out, int n_rows, int I, cudaStream_t s) {
+  return silu_mul<float>(in, out, n_rows, I, s);
+}
+GB_EXPORT int gb_silu_mul_bf16(const void* in, void* out, int n_rows, int I, cudaStream_t s) {
+  return silu_mul<bf16>(in, out, n_rows, I, s);
+}
+
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) out[i] = from_f32<TO>(to_f32<TI>(in[i]));
+}
+template <typename TI, typename TO>
+static int cast(const void* in, void* out, long long n, cudaStream_t s) {
+  if (n < 0) return GB_ERR_BAD_ARG;
+  if (n == 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  cast_kernel<TI, TO><<<(int)blocks, 256, 0, s>>>((const TI*)in, (TO*)out, (size_t)n);
+  return gb_status();
+}
+GB_EXPORT int gb_cast_f32_to_bf16(const void* in, void* out, long long n, cudaStream_t s) {
+  return cast<float, bf16>(in, out, n, s);
+}
+GB_EXPORT int gb_cast_bf16_to_f32(const void* in, void* out, long long n, cudaStream_t s) {
+  return cast<bf16, float>(in, out, n, s);
+}

@@ -1,0 +1,160 @@
+// Per (token, head) preparation of the fused q|k|v projection output:
+// RMSNorm over head_dim with a weight vector shared by all heads (optional),
+// then the half-split rotation of the first `rot_dim` elements (optional), then
+// q goes to q_out and k, v go into the paged cache at the token's position
+// (and/or to a dense kv_out).  The normalised value is not rounded before the
+// rotation: one rounding at the store, as in the reference's
+// qk_norm_rope_kv_prefill_raw_f16 (src/kernels.rs:3415-3732, maths 3576-3652).
+// angle = float(pos) * inv_freq[j] in 32-bit with the accurate sincosf.
+#include "common.cuh"
+
+struct QkPrepareArgs {
+  const void* qkv;       // [n_tokens, (nq + 2 nkv) * D]
+  const void* q_w;       // [D] or null
+  const void* k_w;       // [D] or null
+  const float* inv_freq; // [rot_dim / 2] or null
+  const int* token_seq;  // [n_tokens] index into slots
+  const int* token_pos;  // [n_tokens] absolute position
+  const int* slots;      // [n_seqs], < 0 for a padding row
+  const int* block_table;
+  void* q_out;           // [n_tokens, nq, D]
+  void* kv_out;          // [n_tokens, 2 nkv, D] or null
+  void* k_pages;         // [n_pages, nkv, page, D] or null
+  void* v_pages;
+  float eps;
+  int n_tokens, nq, nkv, D, rot_dim, max_pages, page;
+};
+
+template <typename T, typename WT>
+__global__ void qk_prepare_kernel(const QkPrepareArgs a) {
+  extern __shared__ float sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int n_heads = a.nq + 2 * a.nkv;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (head >= n_heads) return;  // warps are independent below
+  const int D = a.D;
+  float* x = sm + warp * D;
+  const T* src = (const T*)a.qkv + ((size_t)t * n_heads + head) * D;
+  const int kind = head < a.nq ? 0 : (head < a.nq + a.nkv ? 1 : 2);
+  for (int d = lane; d < D; d += 32) x[d] = to_f32<T>(src[d]);
+  __syncwarp();
+  const WT* w = kind == 0 ? (const WT*)a.q_w : (kind == 1 ? (const WT*)a.k_w : nullptr);
+  if (w) {
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) ss += x[d] * x[d];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+    for (int d = lane; d < D; d += 32) x[d] = x[d] * inv * to_f32<WT>(w[d]);
+    __syncwarp();
+  }
+  const int pos = a.token_pos[t];
+  if (kind != 2 && a.inv_freq) {
+    const int half = a.rot_dim / 2;
+    for (int j = lane; j < half; j += 32) {
+      const float angle = (float)pos * a.inv_freq[j];
+      float s, c;
+      sincosf(angle, &s, &c);
+      const float lo = x[j], hi = x[j + half];
+      x[j] = lo * c - hi * s;
+      x[j + half] = hi * c + lo * s;
+    }
+    __syncwarp();
+  }
+  if (kind == 0) {
+    T* dst = (T*)a.q_out + ((size_t)t * a.nq + head) * D;
+    for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(x[d]);
+    return;
+  }
+  const int hh = kind == 1 ? head - a.nq : head - a.nq - a.nkv;
+  if (a.kv_out) {
+    T* dst = (T*)a.kv_out + ((size_t)t * 2 * a.nkv + (kind == 1 ? hh : a.nkv + hh)) * D;
+    for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(x[d]);
+  }
+  if (a.k_pages) {
+    const int slot = a.slots[a.token_seq[t]];
+    if (slot < 0) return;  // padding row: nothing is stored
+    const int* table = a.block_table + (size_t)slot * a.max_pages;
+    T* base = (T*)(kind == 1 ? a.k_pages : a.v_pages);
+    T* dst = base + paged_row(table, pos, hh, a.nkv, a.page, D);
+    for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(x[d]);
+  }
+}
+
+template <typename T, typename WT>
+static int launch(const QkPrepareArgs& a, cudaStream_t stream) {
+  const int warps = 4;
+  const int n_heads = a.nq + 2 * a.nkv;
+  dim3 grid(a.n_tokens, (n_heads + warps - 1) / warps);
+  const size_t smem = (size_t)warps * a.D * sizeof(float);
+  if (smem > 48 * 1024) return GB_ERR_UNSUPPORTED;
+  qk_prepare_kernel<T, WT><<<grid, warps * 32, smem, stream>>>(a);
+  return gb_status();
+}
+
+static int check(const QkPrepareArgs& a) {
+  if (a.n_tokens < 0 || a.nq <= 0 || a.nkv < 0 || a.D <= 0 || !a.qkv || !a.q_out) return GB_ERR_BAD_ARG;
+  if (a.inv_freq && (a.rot_dim <= 0 || a.rot_dim > a.D || (a.rot_dim & 1))) return GB_ERR_BAD_ARG;
+  if (a.k_pages && (!a.v_pages || !a.block_table || !a.slots || !a.token_seq || a.page <= 0 ||
+                    a.max_pages <= 0))
+    return GB_ERR_BAD_ARG;
+  if (!a.token_pos) return GB_ERR_BAD_ARG;
+  return 0;
+}
+
+GB_EXPORT int gb_qk_prepare_f32(const QkPrepareArgs* a, int w_is_f32, cudaStream_t s) {
+  int e = check(*a);
+  if (e) return e;
+  if (a->n_tokens == 0) return 0;
+  if (!w_is_f32) return GB_ERR_UNSUPPORTED;
+  return launch<float, float>(*a, s);
+}
+GB_EXPORT int gb_qk_prepare_bf16(const QkPrepareArgs* a, int w_is_f32, cudaStream_t s) {
+  int e = check(*a);
+  if (e) return e;
+  if (a->n_tokens == 0) return 0;
+  return w_is_f32 ? launch<bf16, float>(*a, s) : launch<bf16, bf16>(*a, s);
+}
+
+// Copies dense k, v rows [n_tokens, 2 nkv, D] into the paged cache: the second
+// half of the work above for position encodings that are applied outside it.
+template <typename T>
+__global__ void kv_write_kernel(const T* __restrict__ kv, const int* token_seq,
+                                const int* token_pos, const int* slots, const int* block_table,
+                                T* k_pages, T* v_pages, int nkv, int D, int max_pages, int page) {
+  const int t = blockIdx.x, hh = blockIdx.y;  // hh in [0, 2 nkv)
+  const int slot = slots[token_seq[t]];
+  if (slot < 0) return;
+  const int* table = block_table + (size_t)slot * max_pages;
+  const bool is_k = hh < nkv;
+  T* dst = (is_k ? k_pages : v_pages) +
+           paged_row(table, token_pos[t], is_k ? hh : hh - nkv, nkv, page, D);
+  const T* src = kv + ((size_t)t * 2 * nkv + hh) * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
+}
+
+template <typename T>
+static int kv_write(const void* kv, const int* token_seq, const int* token_pos, const int* slots,
+                    const int* block_table, void* k_pages, void* v_pages, int n_tokens, int nkv,
+                    int D, int max_pages, int page, cudaStream_t s) {
+  if (n_tokens < 0 || nkv <= 0 || D <= 0 || page <= 0 || max_pages <= 0) return GB_ERR_BAD_ARG;
+  if (n_tokens == 0) return 0;
+  kv_write_kernel<T><<<dim3(n_tokens, 2 * nkv), 64, 0, s>>>(
+      (const T*)kv, token_seq, token_pos, slots, block_table, (T*)k_pages, (T*)v_pages, nkv, D,
+      max_pages, page);
+  return gb_status();
+}
+GB_EXPORT int gb_kv_write_f32(const void* kv, const int* token_seq, const int* token_pos,
+                              const int* slots, const int* block_table, void* k_pages,
+                              void* v_pages, int n_tokens, int nkv, int D, int max_pages, int page,
+                              cudaStream_t s) {
+  return kv_write<float>(kv, token_seq, token_pos, slots, block_table, k_pages, v_pages, n_tokens,
+                         nkv, D, max_pages, page, s);
+}
+GB_EXPORT int gb_kv_write_bf16(const void* kv, const int* token_seq, const int* token_pos,
+                               const int* slots, const int* block_table, void* k_pages,
+                               void* v_pages, int n_tokens, int nkv, int D, int max_pages, int page,
+                               cudaStream_t s) {
+  return kv_write<bf16>(kv, token_seq, token_pos, slots, block_table, k_pages, v_pages, n_tokens,
+                        nkv, D, max_pages, page, s);
+}

@@ -1,0 +1,183 @@
+"""The engine: a model, its cache and the step function, behind one object.
+
+    engine = Engine.load("model_dir", dtype="bfloat16", max_tokens=65536)
+    a = engine.open_sequence()
+    logits = engine.step([(a, [5, 17, 3])], want=[[2]])     # the prompt, in one step
+    logits = engine.step([(a, [42])], want=[[0]])           # then one token
+    engine.close_sequence(a)
+
+``step`` runs exactly the tokens it is given, as one batch, on top of what the
+cache holds for each slot, and returns 32-bit logits at the wanted places.  It
+is the only way tokens reach the model: generation, the command line and trace
+replay all go through it.  (The reference's counterpart is ``step_seq_await``
+for one sequence, src/model.rs:2272-2308.)
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import architectures  # noqa: F401  (registers the known architectures)
+from ..cache import SequenceCache
+from ..config import GenerationConfig, load_config, resolve_architecture
+from ..kernels import build as kernel_build
+from ..parts.base import BuildContext
+from ..weights import DictSource, FolderSource, load_params, random_tensor
+from .batch import make_context
+from .graphs import DecodeGraphs
+from .model import Model
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def _dtype(d) -> torch.dtype:
+    if d not in _DTYPES:
+        raise ValueError(f"dtype must be 'bfloat16' or 'float32', not {d!r}")
+    return _DTYPES[d]
+
+
+def _device(device) -> torch.device:
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        raise RuntimeError(f"device {dev} asked for: this engine runs on a CUDA GPU only "
+                           f"(there is no CPU path)")
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA GPU is visible: this engine has no CPU path")
+    return dev
+
+
+class Engine:
+    DEFAULT_CONTEXT = 4096     # the reference's default context, src/model.rs:1331
+
+    def __init__(self, config, plan, model: Model, dtype: torch.dtype, device: torch.device, *,
+                 max_tokens: Optional[int], max_batch: int, max_seq_len: Optional[int],
+                 use_graphs: Optional[bool], generation_config: Optional[GenerationConfig] = None):
+        self.config, self.plan, self.model = config, plan, model
+        self.dtype, self.device = dtype, device
+        self.generation_config = generation_config
+        # S = min(asked or 4096, max_position_embeddings), src/model.rs:1331
+        self.max_seq_len = min(max_seq_len or self.DEFAULT_CONTEXT, plan.max_position)
+        if max_tokens is None:
+            max_tokens = max_batch * self.max_seq_len
+        self.cache = SequenceCache(model.cache_layout(), max_tokens=max_tokens,
+                                   max_slots=max_batch, max_seq_len=self.max_seq_len,
+                                   dtype=dtype, device=device)
+        self.use_graphs = (dtype == torch.bfloat16) if use_graphs is None else bool(use_graphs)
+        self.graphs = DecodeGraphs(model, self.cache, device)
+        self.vocab_size = plan.vocab_size
+
+    # -- construction --------------------------------------------------------
+    @classmethod
+    def _build(cls, arch, config, source, dtype, device, **kw) -> "Engine":
+        dtype, device = _dtype(dtype), _device(device)
+        torch.cuda.set_device(device)
+        plan = arch.plan(config)
+        model = Model(plan, BuildContext(dtype, device))
+        get = load_params(model.expected(), source, dtype, device)
+        with torch.cuda.device(device):
+            model.load(get)
+        kernel_build.compile_modules(model.kernel_modules())
+        for m in model.kernel_modules():
+            kernel_build.module(m)
+        return cls(config, plan, model, dtype, device, **kw)
+
+    @classmethod
+    def load(cls, model_dir: str, dtype="bfloat16", device="cuda:0", *, max_tokens=None,
+             max_batch: int = 64, max_seq_len=None, use_graphs=None) -> "Engine":
+        """A model folder: config.json chooses the architecture, the safetensors
+        file(s) give the weights."""
+        arch, config = load_config(model_dir)
+        return cls._build(arch, config, FolderSource(model_dir), dtype, device,
+                          max_tokens=max_tokens, max_batch=max_batch, max_seq_len=max_seq_len,
+                          use_graphs=use_graphs,
+                          generation_config=GenerationConfig.from_model_dir(model_dir))
+
+    @classmethod
+    def from_tensors(cls, config: dict, tensors: Dict[str, torch.Tensor], dtype="bfloat16",
+                     device="cuda:0", **kw) -> "Engine":
+        arch = resolve_architecture(config)
+        cfg = arch.config_cls.from_dict(config)
+        kw.setdefault("max_tokens", None), kw.setdefault("max_batch", 64)
+        kw.setdefault("max_seq_len", None), kw.setdefault("use_graphs", None)
+        return cls._build(arch, cfg, DictSource(tensors), dtype, device, **kw)
+
+    @classmethod
+    def random(cls, config: dict, seed: int, dtype="bfloat16", device="cuda:0", **kw) -> "Engine":
+        """Random weights made on the device, tensor by tensor, without a folder
+        (for sizes that are not worth writing to disk)."""
+        arch = resolve_architecture(config)
+        cfg = arch.config_cls.from_dict(config)
+        kw.setdefault("max_tokens", None), kw.setdefault("max_batch", 64)
+        kw.setdefault("max_seq_len", None), kw.setdefault("use_graphs", None)
+        dev = _device(device)
+
+        class _Made(DictSource):
+            def __init__(self, expected):
+                self.expected, self.where = expected, f"random weights (seed {seed})"
+
+            def shapes(self):
+                return {n: s.shape for n, s in self.expected.items()}
+
+            def tensor(self, name):
+                return random_tensor(name, self.expected[name], seed, torch.bfloat16, dev)
+
+        plan = arch.plan(cfg)
+        probe = Model(plan, BuildContext(torch.bfloat16, torch.device("cpu")))
+        return cls._build(arch, cfg, _Made(probe.expected()), dtype, device, **kw)
+
+    # -- sequences -------------------------------------------------------------
+    def open_sequence(self) -> int:
+        return self.cache.open()
+
+    def close_sequence(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length[slot]
+
+    # -- the step --------------------------------------------------------------
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
+        """entries: (slot, next tokens) per sequence; want: per entry, the places
+        among its tokens whose logits are returned ([n_wanted, vocab], float32, in
+        the order of the entries and of ``want``).  None when nothing is wanted."""
+        if not entries:
+            raise ValueError("a step needs at least one sequence")
+        want = [list(w) for w in want] if want is not None else [[] for _ in entries]
+        if len(want) != len(entries):
+            raise ValueError("one list of wanted places per entry is needed")
+        seen = set()
+        for slot, toks in entries:
+            if slot in seen:
+                raise ValueError(f"slot {slot} appears twice in one step")
+            seen.add(slot)
+            if len(toks) == 0:
+                raise ValueError(f"slot {slot} brings no tokens")   # src/model.rs:2286
+            bad = [t for t in toks if not 0 <= int(t) < self.vocab_size]
+            if bad:
+                raise ValueError(f"token {bad[0]} is outside the vocabulary of {self.vocab_size}")
+        for slot, toks in entries:
+            self.cache.reserve(slot, len(toks))
+        self.cache.flush()
+        packed = [(slot, self.cache.length[slot], list(toks)) for slot, toks in entries]
+        decode = all(len(t) == 1 for _s, t in entries)
+        graph = self.graphs.get(len(entries)) if (decode and self.use_graphs) else None
+        with torch.cuda.device(self.device):
+            if graph is not None:
+                all_rows = graph.run(packed)
+                idx = [i for i, w in enumerate(want) for _p in w]
+                if not idx:
+                    logits = None
+                elif idx == list(range(all_rows.shape[0])):
+                    logits = all_rows
+                else:
+                    logits = all_rows[torch.tensor(idx, device=self.device)]
+            else:
+                ctx = make_context(packed, want, self.device)
+                logits = self.model.forward(ctx, self.cache)
+        for slot, toks in entries:
+            self.cache.advance(slot, len(toks))
+        return logits

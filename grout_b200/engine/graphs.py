@@ -1,0 +1,94 @@
+"""The decode step as a CUDA graph, one per batch-size bucket.
+
+A decode step is a few hundred short kernels; launched one by one the host
+cannot keep up with the GPU.  The whole step (embedding to logits) is captured
+once per bucket and replayed.  Everything that changes from step to step —
+tokens, slots, positions, lengths — is read by the kernels from one device
+buffer whose address is fixed and whose contents are refreshed by a single copy
+before each replay; the cache's block tables and pages never move.  Rows beyond
+the live sequences carry slot -1 and store nothing.  (The reference captures its
+single-sequence decode step the same way, src/model.rs:3118-3647, and feeds it
+a position by a 4-byte copy, 363-400.)
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import numpy as np
+import torch
+
+from .batch import context_from, layout_sizes, pack_step
+
+
+def bucket_for(n: int, largest: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b if b <= largest else 0
+
+
+class DecodeGraph:
+    def __init__(self, model, cache, n_seqs: int, device):
+        self.model, self.cache, self.n, self.device = model, cache, n_seqs, device
+        off, total = layout_sizes(n_seqs, n_seqs, n_seqs)
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=device)
+        self.graph = None
+        self.logits = None
+
+    def _fill(self, entries) -> dict:
+        """Packs the live sequences plus padding rows and copies them to the device.
+        Every row's logits are computed: the head reads its weights once anyway."""
+        n_real = len(entries)
+        buf, meta = pack_step(entries, [[0]] * n_real, self.n - n_real)
+        full_off, total = layout_sizes(self.n, self.n, self.n)
+        out = self.host.numpy()
+        out[:] = 0
+        # want_rows is the last array, so all others sit at the same offsets
+        o_want, _ = full_off["want_rows"]
+        out[:o_want] = buf[:o_want]
+        out[o_want:o_want + self.n] = np.arange(self.n, dtype=np.int32)
+        self.dev.copy_(self.host, non_blocking=True)
+        return dict(meta, off=full_off, n_want=self.n)
+
+    def _capture(self) -> None:
+        """Warm-up with padding rows only (which store nothing), then capture."""
+        meta = self._fill([])
+        step = context_from(self.dev, meta)
+        # bounds that kernels size their launches with must hold for every replay
+        step.max_kv_len = self.cache.max_seq_len
+        step.q_lens = step.starts = step.slot_list = ()
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.model.forward(step, self.cache)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.current_stream().synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.logits = self.model.forward(step, self.cache)
+        self.graph = g
+
+    def run(self, entries) -> torch.Tensor:
+        """entries: (slot, start, [token]) of the live sequences, at most n.
+        Returns logits [n, vocab]; rows beyond the live sequences are padding."""
+        if self.graph is None:
+            self._capture()
+        self._fill(entries)
+        self.graph.replay()
+        return self.logits
+
+
+class DecodeGraphs:
+    def __init__(self, model, cache, device, largest: int = 256):
+        self.model, self.cache, self.device, self.largest = model, cache, device, largest
+        self.graphs: Dict[int, DecodeGraph] = {}
+
+    def get(self, n_live: int):
+        b = bucket_for(n_live, self.largest)
+        if not b:
+            return None
+        g = self.graphs.get(b)
+        if g is None:
+            g = self.graphs[b] = DecodeGraph(self.model, self.cache, b, self.device)
+        return g

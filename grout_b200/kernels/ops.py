@@ -1,0 +1,320 @@
+"""Typed, checked entry points of the CUDA kernels.
+
+Each function takes torch CUDA tensors, checks dtype, shape and contiguity,
+and launches the kernel on torch's current stream.  Nothing here computes: a
+tensor that is not on the GPU, or a size a kernel does not take, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional, Tuple
+
+import torch
+
+from .build import module
+
+_P, _I, _F, _L = c_void_p, c_int, c_float, c_longlong
+_CODES = {"p": _P, "i": _I, "f": _F, "l": _L}
+_FUNCS = {}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_OWN_ERRORS = {-1: "the kernel refused its arguments (bad size or pointer)",
+               -2: "no kernel for this combination of sizes and types",
+               -3: "size beyond the kernel's stated maximum"}
+
+
+def _fn(mod: str, name: str, sig: str):
+    key = (mod, name)
+    f = _FUNCS.get(key)
+    if f is None:
+        f = getattr(module(mod), name)
+        f.argtypes = [_CODES[c] for c in sig]
+        f.restype = c_int
+        _FUNCS[key] = f
+    return f
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc in _OWN_ERRORS:
+        raise KernelError(f"{what}: {_OWN_ERRORS[rc]}")
+    raise KernelError(f"{what}: CUDA error {rc} at launch ({_cuda_error_name(rc)})")
+
+
+def _cuda_error_name(rc: int) -> str:
+    try:
+        return str(torch.cuda.cudart().cudaGetErrorString(torch.cuda.cudart().cudaError(rc)))
+    except Exception:
+        return "cudaError_t value"
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _suffix(dtype: torch.dtype) -> str:
+    if dtype == torch.float32:
+        return "f32"
+    if dtype == torch.bfloat16:
+        return "bf16"
+    raise KernelError(f"kernels take float32 or bfloat16 activations, not {dtype}")
+
+
+def _need(t: Optional[torch.Tensor], name: str, dtype=None, ndim=None) -> None:
+    if t is None:
+        raise KernelError(f"{name} is missing")
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor: there is no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, found {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dimensions, found {tuple(t.shape)}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+# ---------------------------------------------------------------- embedding
+def embed(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    _need(table, "embedding table", ndim=2)
+    _need(ids, "token ids", torch.int32, 1)
+    V, H = table.shape
+    out = torch.empty((ids.shape[0], H), dtype=table.dtype, device=table.device)
+    sfx = _suffix(table.dtype)
+    _check(_fn("embed", f"gb_embed_{sfx}", "pppiiip")(
+        table.data_ptr(), ids.data_ptr(), out.data_ptr(), ids.shape[0], H, V, _stream()), "embed")
+    return out
+
+
+# ---------------------------------------------------------------- norm
+def add_rmsnorm(res_in: Optional[torch.Tensor], delta: Optional[torch.Tensor],
+                weight: torch.Tensor, eps: float, *, dtype: torch.dtype,
+                rows: Optional[torch.Tensor] = None, write_res: bool = True
+                ) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+    """(res_in + delta) in 32-bit -> (residual, normed).  Without ``rows`` the
+    residual is updated in place when ``res_in`` is given."""
+    src = res_in if res_in is not None else delta
+    if src is None:
+        raise KernelError("add_rmsnorm needs a residual or a delta")
+    if res_in is not None:
+        _need(res_in, "residual", torch.float32, 2)
+    if delta is not None:
+        _need(delta, "delta", dtype, 2)
+        if res_in is not None and delta.shape != res_in.shape:
+            raise KernelError(f"residual {tuple(res_in.shape)} and delta {tuple(delta.shape)} differ")
+    _need(weight, "norm weight", ndim=1)
+    N = src.shape[1]
+    if weight.shape[0] != N:
+        raise KernelError(f"norm weight has {weight.shape[0]} elements for rows of {N}")
+    w_is_f32 = weight.dtype == torch.float32
+    if not w_is_f32 and weight.dtype != dtype:
+        raise KernelError(f"norm weight must be float32 or {dtype}, found {weight.dtype}")
+    if rows is not None:
+        _need(rows, "row list", torch.int32, 1)
+        n_rows = rows.shape[0]
+    else:
+        n_rows = src.shape[0]
+    res_out = None
+    if write_res:
+        if rows is None and res_in is not None:
+            res_out = res_in
+        else:
+            res_out = torch.empty((n_rows, N), dtype=torch.float32, device=src.device)
+    y = torch.empty((n_rows, N), dtype=dtype, device=src.device)
+    sfx = _suffix(dtype)
+    _check(_fn("norm", f"gb_add_rmsnorm_{sfx}", "ppppifppiip")(
+        _ptr(res_in), _ptr(delta), _ptr(rows), weight.data_ptr(), int(w_is_f32), float(eps),
+        _ptr(res_out), y.data_ptr(), n_rows, N, _stream()), "add_rmsnorm")
+    return res_out, y
+
+
+# ---------------------------------------------------------------- q/k preparation
+class _QkPrepareArgs(ctypes.Structure):
+    _fields_ = [("qkv", _P), ("q_w", _P), ("k_w", _P), ("inv_freq", _P), ("token_seq", _P),
+                ("token_pos", _P), ("slots", _P), ("block_table", _P), ("q_out", _P),
+                ("kv_out", _P), ("k_pages", _P), ("v_pages", _P), ("eps", _F),
+                ("n_tokens", _I), ("nq", _I), ("nkv", _I), ("D", _I), ("rot_dim", _I),
+                ("max_pages", _I), ("page", _I)]
+
+
+def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=None,
+               eps: float = 0.0, inv_freq=None, rot_dim: int = 0, token_seq, token_pos, slots,
+               block_table=None, k_pages=None, v_pages=None, page: int = 0,
+               want_kv_out: bool = False):
+    """Returns (q [T, nq, D], kv_out or None); writes k, v into the pages when given."""
+    _need(qkv, "qkv", ndim=2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * D:
+        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected (nq + 2 nkv) * D = "
+                          f"{(nq + 2 * nkv) * D}")
+    dt = qkv.dtype
+    w_is_f32 = 0
+    for w, nm in ((q_w, "q norm weight"), (k_w, "k norm weight")):
+        if w is not None:
+            _need(w, nm, ndim=1)
+            if w.shape[0] != D:
+                raise KernelError(f"{nm} has {w.shape[0]} elements for head_dim {D}")
+            w_is_f32 = int(w.dtype == torch.float32)
+    if q_w is not None and k_w is not None and q_w.dtype != k_w.dtype:
+        raise KernelError("q and k norm weights must have one dtype")
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] * 2 != rot_dim:
+            raise KernelError("inv_freq must hold rot_dim / 2 entries")
+    _need(token_pos, "token_pos", torch.int32, 1)
+    _need(token_seq, "token_seq", torch.int32, 1)
+    _need(slots, "slots", torch.int32, 1)
+    q = torch.empty((T, nq, D), dtype=dt, device=qkv.device)
+    kv_out = torch.empty((T, 2 * nkv, D), dtype=dt, device=qkv.device) if want_kv_out else None
+    a = _QkPrepareArgs()
+    a.qkv, a.q_w, a.k_w, a.inv_freq = qkv.data_ptr(), _ptr(q_w), _ptr(k_w), _ptr(inv_freq)
+    a.token_seq, a.token_pos, a.slots = token_seq.data_ptr(), token_pos.data_ptr(), slots.data_ptr()
+    a.q_out, a.kv_out = q.data_ptr(), _ptr(kv_out)
+    a.eps, a.n_tokens, a.nq, a.nkv, a.D, a.rot_dim = float(eps), T, nq, nkv, D, int(rot_dim)
+    if k_pages is not None:
+        _need(k_pages, "k pages", dt, 4)
+        _need(v_pages, "v pages", dt, 4)
+        _need(block_table, "block table", torch.int32, 2)
+        if tuple(k_pages.shape[1:]) != (nkv, page, D) or v_pages.shape != k_pages.shape:
+            raise KernelError(f"pages are {tuple(k_pages.shape)}, expected [*, {nkv}, {page}, {D}]")
+        a.block_table, a.k_pages, a.v_pages = block_table.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr()
+        a.max_pages, a.page = block_table.shape[1], page
+    sfx = _suffix(dt)
+    f = _fn("qk_prepare", f"gb_qk_prepare_{sfx}", "pip")
+    _check(f(ctypes.addressof(a), w_is_f32, _stream()), "qk_prepare")
+    return q, kv_out
+
+
+def kv_write(kv: torch.Tensor, nkv: int, D: int, *, token_seq, token_pos, slots, block_table,
+             k_pages, v_pages, page: int) -> None:
+    _need(kv, "kv rows", ndim=3)
+    if tuple(kv.shape[1:]) != (2 * nkv, D):
+        raise KernelError(f"kv rows are {tuple(kv.shape)}, expected [T, {2 * nkv}, {D}]")
+    _need(k_pages, "k pages", kv.dtype, 4)
+    _need(v_pages, "v pages", kv.dtype, 4)
+    _need(block_table, "block table", torch.int32, 2)
+    sfx = _suffix(kv.dtype)
+    _check(_fn("qk_prepare", f"gb_kv_write_{sfx}", "pppppppiiiiip")(
+        kv.data_ptr(), token_seq.data_ptr(), token_pos.data_ptr(), slots.data_ptr(),
+        block_table.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), kv.shape[0], nkv, D,
+        block_table.shape[1], page, _stream()), "kv_write")
+
+
+# ---------------------------------------------------------------- attention
+def _attn_common(q, k_pages, v_pages, block_table, token_seq, token_pos, slots, page):
+    _need(q, "q", ndim=3)
+    T, nq, D = q.shape
+    _need(k_pages, "k pages", q.dtype, 4)
+    _need(v_pages, "v pages", q.dtype, 4)
+    nkv = k_pages.shape[1]
+    if tuple(k_pages.shape[1:]) != (nkv, page, D) or v_pages.shape != k_pages.shape:
+        raise KernelError(f"pages are {tuple(k_pages.shape)}, expected [*, nkv, {page}, {D}]")
+    if nq % nkv:
+        raise KernelError(f"{nq} query heads cannot share {nkv} kv heads")
+    _need(block_table, "block table", torch.int32, 2)
+    _need(token_seq, "token_seq", torch.int32, 1)
+    _need(token_pos, "token_pos", torch.int32, 1)
+    _need(slots, "slots", torch.int32, 1)
+    return T, nq, nkv, D
+
+
+def attn_generic(q, k_pages, v_pages, block_table, *, token_seq, token_pos, slots, page: int,
+                 scale: float, window: Optional[int] = None) -> torch.Tensor:
+    T, nq, nkv, D = _attn_common(q, k_pages, v_pages, block_table, token_seq, token_pos, slots, page)
+    out = torch.empty_like(q)
+    sfx = _suffix(q.dtype)
+    _check(_fn("attn_generic", f"gb_attn_generic_{sfx}", "ppppippppiiiiifip")(
+        q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+        block_table.shape[1], token_seq.data_ptr(), token_pos.data_ptr(), slots.data_ptr(),
+        out.data_ptr(), T, nq, nkv, D, page, float(scale), int(window or 0), _stream()),
+        "attn_generic")
+    return out
+
+
+# ---------------------------------------------------------------- matrix products
+def gemm_f32(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """a [M, K] . w [N, K]^T in true 32-bit on the CUDA cores."""
+    _need(a, "activations", torch.float32, 2)
+    _need(w, "weight", torch.float32, 2)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"weight is {tuple(w.shape)} for activations of width {K}")
+    c = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    _check(_fn("gemm_f32", "gb_gemm_nt_f32", "pppiiiiiip")(
+        a.data_ptr(), w.data_ptr(), c.data_ptr(), M, N, K, K, K, N, _stream()), "gemm_f32")
+    return c
+
+
+# ---------------------------------------------------------------- elementwise
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    _need(gate_up, "gate|up", ndim=2)
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("gate|up must have an even number of columns")
+    out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    sfx = _suffix(gate_up.dtype)
+    _check(_fn("elementwise", f"gb_silu_mul_{sfx}", "ppiip")(
+        gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, _stream()), "silu_mul")
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    _need(x, "tensor")
+    if x.dtype == dtype:
+        return x
+    pair = {(torch.float32, torch.bfloat16): "gb_cast_f32_to_bf16",
+            (torch.bfloat16, torch.float32): "gb_cast_bf16_to_f32"}.get((x.dtype, dtype))
+    if pair is None:
+        raise KernelError(f"no conversion kernel from {x.dtype} to {dtype}")
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _check(_fn("elementwise", pair, "pplp")(x.data_ptr(), out.data_ptr(), x.numel(), _stream()),
+           "cast")
+    return out
+
+
+SKINNY_MAX_ROWS = 64
+
+
+def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """x [M <= 64, K] . w [N, K]^T, bf16 in, 32-bit accumulate; the decode-time linear."""
+    _need(x, "activations", torch.bfloat16, 2)
+    _need(w, "weight", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"weight is {tuple(w.shape)} for activations of width {K}")
+    if M > SKINNY_MAX_ROWS:
+        raise KernelError(f"gemm_skinny_bf16 takes at most {SKINNY_MAX_ROWS} rows, got {M}")
+    if K % 8:
+        raise KernelError(f"gemm_skinny_bf16 needs an inner size that is a multiple of 8, got {K}")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"output must be bfloat16 or float32, not {out_dtype}")
+    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _check(_fn("gemm_skinny_bf16", "gb_gemm_skinny_bf16", "pppiiiip")(
+        x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, int(out_dtype == torch.float32),
+        _stream()), "gemm_skinny_bf16")
+    return y
+
+
+# ---------------------------------------------------------------- attention dispatch
+FAST_ATTENTION_MODULES: Tuple[str, ...] = ()
+
+
+def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float,
+              window: Optional[int] = None) -> torch.Tensor:
+    """Attention of the step's queries over their sequences' cached keys.
+    32-bit tensors take the plain 32-bit kernel; bfloat16 takes the fast kernels
+    where they accept the shape and the plain kernel elsewhere."""
+    return attn_generic(q, k_pages, v_pages, block_table, token_seq=step.token_seq,
+                        token_pos=step.token_pos, slots=step.slots, page=page, scale=scale,
+                        window=window)

@@ -1,0 +1,47 @@
+"""Feed-forward parts.  Interface of the family: ``forward(x, step) -> y`` with
+``x`` and ``y`` [T, hidden] in the compute dtype.  A feed-forward with experts
+routes inside ``forward``; the rows' packing is the step's and does not change.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import BuildContext, ParamSpec, Part, register_part
+from .linear import Linear
+
+
+class FeedForward(Part):
+    family = "feedforward"
+
+    def forward(self, x, step):
+        raise NotImplementedError
+
+
+@register_part("feedforward", "swiglu")
+class SwiGLU(FeedForward):
+    """d = (silu(x Wg^T) * (x Wu^T)) Wd^T, no biases (src/training.rs:344-349).
+    Gate and up are fused into one product at load (src/model.rs:1401)."""
+
+    def __init__(self, ctx: BuildContext, hidden: int, intermediate: int):
+        super().__init__(ctx)
+        self.hidden, self.intermediate = int(hidden), int(intermediate)
+        self.gate_up = self.down = None
+
+    def param_specs(self):
+        return {"gate_proj.weight": ParamSpec((self.intermediate, self.hidden)),
+                "up_proj.weight": ParamSpec((self.intermediate, self.hidden)),
+                "down_proj.weight": ParamSpec((self.hidden, self.intermediate))}
+
+    def load(self, params):
+        g, u = params["gate_proj.weight"], params["up_proj.weight"]
+        if g.dtype != u.dtype:
+            raise ValueError("gate and up projections must be stored in one dtype to be fused")
+        self.gate_up = Linear(torch.cat([g, u], dim=0))
+        self.down = Linear(params["down_proj.weight"])
+
+    def kernel_modules(self):
+        return ("elementwise",) + self.gate_up.kernel_modules() + self.down.kernel_modules()
+
+    def forward(self, x, step):
+        return self.down(ops.silu_mul(self.gate_up(x)))

@@ -1,0 +1,49 @@
+"""y = x W^T with W stored [out, in], the one linear layer every part uses.
+
+It picks the product by the weight's precision and by the number of rows:
+
+* 32-bit weight: the true 32-bit CUDA-core product (``gemm_f32``); bf16
+  activations are widened first and the result narrowed, so a tensor that the
+  checkpoint stores in 32-bit is used in 32-bit.
+* bf16 weight, up to 64 rows: the hand-written weight-streaming kernel
+  (``gemm_skinny_bf16``) — every decode step.
+* bf16 weight, more rows: the library's matrix product, which is where the
+  reference uses a library too (cuBLAS GemmEx, src/cublas.rs:287-307).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor):
+        if weight.dim() != 2:
+            raise ValueError(f"a linear weight is [out, in], got {tuple(weight.shape)}")
+        if weight.dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"a linear weight is float32 or bfloat16, got {weight.dtype}")
+        self.weight = weight.contiguous()
+        self.out_features, self.in_features = weight.shape
+
+    def kernel_modules(self):
+        if self.weight.dtype == torch.float32:
+            return ("gemm_f32", "elementwise")
+        return ("gemm_skinny_bf16",)
+
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        out_dtype = out_dtype or x.dtype
+        w = self.weight
+        if w.dtype == torch.float32:
+            y = ops.gemm_f32(ops.cast(x, torch.float32), w)
+            return ops.cast(y, out_dtype)
+        if x.dtype != torch.bfloat16:
+            raise ops.KernelError("a bfloat16 weight takes bfloat16 activations")
+        M = x.shape[0]
+        if M <= ops.SKINNY_MAX_ROWS and self.in_features % 8 == 0:
+            return ops.gemm_skinny_bf16(x, w, out_dtype)
+        if out_dtype == torch.float32:
+            return torch.mm(x, w.t(), out_dtype=torch.float32)
+        return torch.mm(x, w.t())

@@ -1,0 +1,123 @@
+"""The engine against the plain implementation, in every way of cutting the work."""
+import pytest
+import torch
+
+from conftest import TINY, random_tokens
+from helpers import assert_close, run_batch, run_tail_decoded, run_whole
+from plain import qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"A": [5, 70, 128], "B": [1, 7, 64, 150], "C": [33, 130, 300]}
+
+
+@pytest.fixture(scope="module")
+def engines(model_dirs):
+    from grout_b200.engine import Engine
+    made = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in made:
+            made[(name, dtype)] = Engine.load(model_dirs[name], dtype=dtype, max_tokens=4096,
+                                              max_batch=8, max_seq_len=512)
+        return made[(name, dtype)]
+    return get
+
+
+@pytest.fixture(scope="module")
+def oracle(plain_weights):
+    memo = {}
+
+    def get(name, tokens):
+        key = (name, tuple(tokens))
+        if key not in memo:
+            cfg, w = plain_weights[name]
+            memo[key] = plain.logits(w, cfg, list(tokens))
+        return memo[key]
+    return get
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_each_request_alone_and_whole(engines, oracle, name, dtype):
+    eng = engines(name, dtype)
+    for i, n in enumerate(LENGTHS[name]):
+        toks = random_tokens(n, TINY[name]["vocab_size"], 100 + i)
+        assert_close(run_whole(eng, toks), oracle(name, toks), dtype, f"{name} whole, {n} tokens")
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0 and eng.cache.tokens_held() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_last_32_tokens_one_by_one(engines, oracle, name, dtype):
+    eng = engines(name, dtype)
+    for i, n in enumerate(LENGTHS[name][1:]):
+        toks = random_tokens(n, TINY[name]["vocab_size"], 200 + i)
+        assert_close(run_tail_decoded(eng, toks), oracle(name, toks), dtype,
+                     f"{name} tail decoded, {n} tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_unequal_batches_one_after_another(engines, oracle, name, dtype):
+    """Three batches in a row on the same engine, so that slots and pages of an
+    earlier batch are used again by a later one; within a batch the shorter
+    requests end earlier."""
+    eng = engines(name, dtype)
+    V, top = TINY[name]["vocab_size"], TINY[name]["max_position_embeddings"]
+    plans = [[(5, 3), (11, 9), (17, 1)],
+             [(1, 20), (7, 2), (30, 11), (64, 5), (min(top - 40, 130), 33)],
+             [(65, 4), (2, 4)]]
+    used = []
+    for b, plan in enumerate(plans):
+        reqs = [random_tokens(p + d, V, 300 + 10 * b + i) for i, (p, d) in enumerate(plan)]
+        got = run_batch(eng, reqs, [p for p, _ in plan])
+        for i, r in enumerate(reqs):
+            assert_close(got[i], oracle(name, r), dtype, f"{name} batch {b} request {i}")
+        eng.cache.check()
+        assert eng.cache.slots.n_held == 0
+        used.append(True)
+    assert len(used) == 3
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens_and_long_decoding(engines, oracle, dtype):
+    """A prompt of one token followed by 140 decoded tokens: the first positions
+    of a sequence and a long run of single steps across two page boundaries."""
+    eng = engines("B", dtype)
+    toks = random_tokens(141, TINY["B"]["vocab_size"], 400)
+    assert_close(run_tail_decoded(eng, toks, tail=140), oracle("B", toks), dtype, "long decoding")
+
+
+def test_fp32_cuts_agree_tightly(engines):
+    """Whole, tail-decoded and batched runs of the 32-bit path differ by rounding
+    only; a looser agreement would point at the cache or the batch."""
+    eng = engines("B", "float32")
+    toks = random_tokens(100, TINY["B"]["vocab_size"], 500)
+    other = random_tokens(37, TINY["B"]["vocab_size"], 501)
+    whole = run_whole(eng, toks)
+    tail = run_tail_decoded(eng, toks)
+    batch = run_batch(eng, [other, toks], [5, 60])[1]
+    assert (whole - tail).abs().max().item() < 2e-6
+    assert (whole - batch).abs().max().item() < 2e-6
+
+
+def test_padding_changes_nothing(engines):
+    """A decode step through the captured graph (padded to a bucket) gives what
+    the same step gives without a graph."""
+    from grout_b200.engine import Engine
+    eng = engines("A", "bfloat16")
+    toks = [random_tokens(20 + i, 256, 600 + i) for i in range(3)]
+    outs = []
+    for use in (True, False):
+        eng.use_graphs = use
+        slots = [eng.open_sequence() for _ in toks]
+        eng.step([(s, t[:-1]) for s, t in zip(slots, toks)])
+        outs.append(eng.step([(s, [t[-1]]) for s, t in zip(slots, toks)],
+                             [[0]] * 3).float().cpu())
+        for s in slots:
+            eng.close_sequence(s)
+    eng.use_graphs = True
+    assert torch.equal(outs[0], outs[1])

@@ -1,0 +1,277 @@
+"""Each kernel alone against a plain 64-bit computation of the same operation,
+at sizes other than the tiny models' (odd widths, head sizes in steps of 16,
+many groups, scattered pages)."""
+import math
+
+import pytest
+import torch
+
+from plain import qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def _ops():
+    from grout_b200.kernels import ops
+    return ops
+
+
+def _rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def _eps(dtype):
+    return 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -22
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_embed(dtype):
+    dt = DT[dtype]
+    table = _rand((1000, 72), dt, 1)
+    ids = torch.tensor([0, 999, 5, 5, 317], dtype=torch.int32)
+    got = _ops().embed(table.to(DEV), ids.to(DEV)).cpu()
+    assert torch.equal(got, table[ids.long()])
+    # a width that is no multiple of 16 bytes takes the scalar path
+    table = _rand((50, 7), dt, 2)
+    got = _ops().embed(table.to(DEV), ids[:3].clamp(max=49).to(DEV)).cpu()
+    assert torch.equal(got, table[ids[:3].clamp(max=49).long()])
+
+
+@pytest.mark.parametrize("w32", [False, True])
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("N", [200, 2560, 5000])
+def test_add_rmsnorm(dtype, N, w32):
+    dt = DT[dtype]
+    if dtype == "float32" and not w32:
+        pytest.skip("32-bit activations take 32-bit weights")
+    rows = 9
+    res = _rand((rows, N), torch.float32, 3)
+    delta = _rand((rows, N), dt, 4)
+    w = (1 + 0.1 * _rand((N,), torch.float32, 5)).to(torch.float32 if w32 else dt)
+    eps = 1e-5
+    want_res = res.double() + delta.double()
+    want_y = plain.rms_norm(want_res, w, eps)
+    r = res.clone().to(DEV)
+    res_out, y = _ops().add_rmsnorm(r, delta.to(DEV), w.to(DEV), eps, dtype=dt)
+    assert res_out.data_ptr() == r.data_ptr()
+    assert torch.allclose(res_out.cpu().double(), want_res, atol=1e-6, rtol=1e-6)
+    assert torch.allclose(y.cpu().double(), want_y, atol=4 * _eps(dt), rtol=2 * _eps(dt))
+    # gathered rows, first-layer form (no residual yet) and plain norm
+    idx = torch.tensor([8, 0, 3], dtype=torch.int32)
+    res2, y2 = _ops().add_rmsnorm(res.to(DEV), delta.to(DEV), w.to(DEV), eps, dtype=dt,
+                                  rows=idx.to(DEV))
+    assert torch.allclose(res2.cpu().double(), want_res[idx.long()], atol=1e-6, rtol=1e-6)
+    assert torch.allclose(y2.cpu().double(), want_y[idx.long()], atol=4 * _eps(dt), rtol=2 * _eps(dt))
+    res3, y3 = _ops().add_rmsnorm(None, delta.to(DEV), w.to(DEV), eps, dtype=dt)
+    assert torch.equal(res3.cpu(), delta.float())
+    assert torch.allclose(y3.cpu().double(), plain.rms_norm(delta.double(), w, eps),
+                          atol=4 * _eps(dt), rtol=2 * _eps(dt))
+
+
+class Paged:
+    """Sequences laid out in scattered pages, with the dense copies for the oracle."""
+
+    def __init__(self, lens, nkv, D, dtype, seed, page=64, spare=5):
+        g = torch.Generator().manual_seed(seed)
+        self.page, self.nkv, self.D = page, nkv, D
+        n_need = sum((n + page - 1) // page for n in lens)
+        n_pages = n_need + spare
+        perm = torch.randperm(n_pages, generator=g).tolist()
+        self.max_pages = max((n + page - 1) // page for n in lens) + 1
+        # slots are scattered too: sequence i lives in slot slot_of[i]
+        self.n_slots = len(lens) + 2
+        self.slot_of = torch.randperm(self.n_slots, generator=g).tolist()[:len(lens)]
+        self.table = torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32)
+        self.k_pages = torch.full((n_pages, nkv, page, D), float("nan")).to(dtype)
+        self.v_pages = torch.full((n_pages, nkv, page, D), float("nan")).to(dtype)
+        self.k, self.v = [], []
+        for i, n in enumerate(lens):
+            k = (torch.randn((n, nkv, D), generator=g)).to(dtype)
+            v = (torch.randn((n, nkv, D), generator=g)).to(dtype)
+            self.k.append(k)
+            self.v.append(v)
+            for p in range((n + page - 1) // page):
+                pg = perm.pop()
+                self.table[self.slot_of[i], p] = pg
+                m = min(page, n - p * page)
+                self.k_pages[pg, :, :m] = k[p * page:p * page + m].transpose(0, 1)
+                self.v_pages[pg, :, :m] = v[p * page:p * page + m].transpose(0, 1)
+
+    def store(self, i, pos, k_row, v_row):
+        pg = int(self.table[self.slot_of[i], pos // self.page])
+        self.k_pages[pg, :, pos % self.page] = k_row
+        self.v_pages[pg, :, pos % self.page] = v_row
+
+
+def _attn_oracle(q, k, v, pos, scale, window):
+    """q [nq, D] at absolute position pos over keys k, v [n, nkv, D]."""
+    nq, D = q.shape
+    nkv = k.shape[1]
+    out = torch.empty(nq, D, dtype=torch.float64)
+    lo = 0 if window is None else max(0, pos - window + 1)
+    for h in range(nq):
+        kh, vh = k[lo:pos + 1, h // (nq // nkv)].double(), v[lo:pos + 1, h // (nq // nkv)].double()
+        s = (kh @ q[h].double()) * scale
+        p = torch.softmax(s, 0)
+        out[h] = p @ vh
+    return out
+
+
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("nq,nkv,D", [(6, 2, 48), (8, 1, 128), (3, 3, 16)])
+def test_attn_generic(dtype, nq, nkv, D, window):
+    dt = DT[dtype]
+    lens = [1, 130, 200, 64]
+    pc = Paged(lens, nkv, D, dt, 7)
+    # queries: every sequence's last position, plus inner positions of sequence 2
+    places = [(0, 0), (1, 129), (2, 199), (3, 63), (2, 0), (2, 63), (2, 64), (2, 127), (2, 128)]
+    q = _rand((len(places), nq, D), dt, 8)
+    scale = 1.0 / math.sqrt(D)
+    # the far key among hundreds: scale one query and one early key so that its
+    # score stands out; the output must then be that key's value
+    far_q, far_seq, far_key = 2, 2, 3
+    if window is None:
+        q[far_q] = 0
+        q[far_q, :, 0] = 30.0
+        pc.k[far_seq][:, :, 0] = 0
+        pc.k[far_seq][far_key, :, 0] = 30.0
+        pc.store(far_seq, far_key, pc.k[far_seq][far_key], pc.v[far_seq][far_key])
+        for j in range(lens[far_seq]):
+            pc.store(far_seq, j, pc.k[far_seq][j], pc.v[far_seq][j])
+    slots = torch.tensor(pc.slot_of, dtype=torch.int32)
+    token_seq = torch.tensor([s for s, _ in places], dtype=torch.int32)
+    token_pos = torch.tensor([p for _, p in places], dtype=torch.int32)
+    got = _ops().attn_generic(q.to(DEV), pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV),
+                              token_seq=token_seq.to(DEV), token_pos=token_pos.to(DEV),
+                              slots=slots.to(DEV), page=64, scale=scale, window=window).cpu()
+    for r, (s, p) in enumerate(places):
+        want = _attn_oracle(q[r], pc.k[s], pc.v[s], p, scale, window)
+        assert torch.allclose(got[r].double(), want, atol=6 * _eps(dt), rtol=4 * _eps(dt)), (r, s, p)
+    if window is None:
+        h = 0
+        want = pc.v[far_seq][far_key, 0].double()
+        assert torch.allclose(got[far_q, h].double(), want, atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("nq,nkv,D,rot", [(6, 2, 48, 48), (4, 4, 64, 32), (8, 1, 128, 128)])
+def test_qk_prepare(dtype, nq, nkv, D, rot):
+    dt = DT[dtype]
+    theta, eps = 50000.0, 1e-5
+    lens = [3, 70]
+    pc = Paged(lens, nkv, D, dt, 11)
+    # tokens: the last two of sequence 0 and three of sequence 1 across a page edge
+    places = [(0, 1), (0, 2), (1, 63), (1, 64), (1, 69)]
+    T = len(places)
+    qkv = _rand((T, (nq + 2 * nkv) * D), dt, 12)
+    q_w = (1 + 0.1 * _rand((D,), torch.float32, 13)).to(dt)
+    k_w = (1 + 0.1 * _rand((D,), torch.float32, 14)).to(dt)
+    inv = torch.from_numpy(plain.rope_inv_freq(rot, theta))
+    pos = [p for _, p in places]
+    x = qkv.double().view(T, nq + 2 * nkv, D)
+    qn = plain.rms_norm(x[:, :nq], q_w, eps)
+    kn = plain.rms_norm(x[:, nq:nq + nkv], k_w, eps)
+    cos, sin = plain.rope_cos_sin(pos, rot, theta)
+    want_q = torch.cat([plain.apply_rope(qn[..., :rot], cos, sin), qn[..., rot:]], -1)
+    want_k = torch.cat([plain.apply_rope(kn[..., :rot], cos, sin), kn[..., rot:]], -1)
+    want_v = x[:, nq + nkv:]
+    kp, vp = pc.k_pages.to(DEV), pc.v_pages.to(DEV)
+    before_k = kp.clone()
+    q, kv = _ops().qk_prepare(
+        qkv.to(DEV), nq, nkv, D, q_w=q_w.to(DEV), k_w=k_w.to(DEV), eps=eps, inv_freq=inv.to(DEV),
+        rot_dim=rot, token_seq=torch.tensor([s for s, _ in places], dtype=torch.int32, device=DEV),
+        token_pos=torch.tensor(pos, dtype=torch.int32, device=DEV),
+        slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
+        block_table=pc.table.to(DEV), k_pages=kp, v_pages=vp, page=64, want_kv_out=True)
+    tol = dict(atol=6 * _eps(dt), rtol=4 * _eps(dt))
+    assert torch.allclose(q.cpu().double(), want_q, **tol)
+    assert torch.allclose(kv.cpu().double()[:, :nkv], want_k, **tol)
+    assert torch.equal(kv.cpu()[:, nkv:], qkv.view(T, -1, D)[:, nq + nkv:])
+    touched = torch.zeros(kp.shape[0], kp.shape[2], dtype=torch.bool)
+    for r, (s, p) in enumerate(places):
+        pg = int(pc.table[pc.slot_of[s], p // 64])
+        touched[pg, p % 64] = True
+        assert torch.allclose(kp[pg, :, p % 64].cpu().double(), want_k[r], **tol)
+        assert torch.allclose(vp[pg, :, p % 64].cpu().double(), want_v[r], **tol)
+    # nothing else in the cache was written
+    same = (kp.cpu().view(torch.int16 if dt == torch.bfloat16 else torch.int32) ==
+            before_k.cpu().view(torch.int16 if dt == torch.bfloat16 else torch.int32)).all(-1).all(1)
+    assert bool(same[~touched].all())
+
+
+def test_qk_prepare_skips_padding_rows():
+    nq, nkv, D = 4, 2, 32
+    pc = Paged([5], nkv, D, torch.bfloat16, 15)
+    kp, vp = pc.k_pages.to(DEV), pc.v_pages.to(DEV)
+    before = kp.clone().view(torch.int16)
+    qkv = _rand((1, (nq + 2 * nkv) * D), torch.bfloat16, 16).to(DEV)
+    _ops().qk_prepare(qkv, nq, nkv, D, token_seq=torch.zeros(1, dtype=torch.int32, device=DEV),
+                      token_pos=torch.zeros(1, dtype=torch.int32, device=DEV),
+                      slots=torch.tensor([-1], dtype=torch.int32, device=DEV),
+                      block_table=pc.table.to(DEV), k_pages=kp, v_pages=vp, page=64)
+    assert torch.equal(kp.view(torch.int16), before)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 130, 100), (70, 65, 17), (129, 200, 333)])
+def test_gemm_f32(M, N, K):
+    a, w = _rand((M, K), torch.float32, 20), _rand((N, K), torch.float32, 21)
+    got = _ops().gemm_f32(a.to(DEV), w.to(DEV)).cpu()
+    want = a.double() @ w.double().T
+    assert torch.allclose(got.double(), want, atol=1e-5 * math.sqrt(K), rtol=1e-5)
+
+
+def test_gemm_f32_row_independent():
+    """A row's result does not depend on the rows beside it (bitwise)."""
+    a, w = _rand((70, 96), torch.float32, 22), _rand((50, 96), torch.float32, 23)
+    full = _ops().gemm_f32(a.to(DEV), w.to(DEV)).cpu()
+    one = _ops().gemm_f32(a[33:34].contiguous().to(DEV), w.to(DEV)).cpu()
+    assert torch.equal(full[33:34], one)
+
+
+@pytest.mark.parametrize("out", ["bfloat16", "float32"])
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16, 27, 33, 64])
+@pytest.mark.parametrize("N,K", [(200, 264), (77, 2560), (2560, 96)])
+def test_gemm_skinny_bf16(M, N, K, out):
+    x, w = _rand((M, K), torch.bfloat16, 24), _rand((N, K), torch.bfloat16, 25, 0.05)
+    got = _ops().gemm_skinny_bf16(x.to(DEV), w.to(DEV), DT[out]).cpu()
+    want = x.double() @ w.double().T
+    e = _eps(DT[out])
+    assert torch.allclose(got.double(), want, atol=2e-5 * math.sqrt(K) + 2 * e, rtol=2 * e)
+
+
+def test_gemm_skinny_row_independent():
+    x, w = _rand((16, 512), torch.bfloat16, 26), _rand((300, 512), torch.bfloat16, 27)
+    full = _ops().gemm_skinny_bf16(x.to(DEV), w.to(DEV), torch.float32).cpu()
+    one = _ops().gemm_skinny_bf16(x[9:10].contiguous().to(DEV), w.to(DEV), torch.float32).cpu()
+    assert torch.equal(full[9:10], one)
+
+
+def test_gemm_skinny_refuses():
+    ops = _ops()
+    x, w = _rand((2, 100), torch.bfloat16, 28).to(DEV), _rand((8, 100), torch.bfloat16, 29).to(DEV)
+    with pytest.raises(ops.KernelError):
+        ops.gemm_skinny_bf16(x, w)            # inner size not a multiple of 8
+    with pytest.raises(ops.KernelError):
+        ops.gemm_skinny_bf16(torch.zeros((65, 96), dtype=torch.bfloat16, device=DEV),
+                             torch.zeros((8, 96), dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(ops.KernelError):
+        ops.gemm_skinny_bf16(x.cpu(), w.cpu())   # no CPU path
+
+
+@pytest.mark.parametrize("dtype", list(DT))
+def test_silu_mul_and_cast(dtype):
+    dt = DT[dtype]
+    gu = _rand((7, 2 * 301), dt, 30, 3.0)
+    got = _ops().silu_mul(gu.to(DEV)).cpu()
+    g, u = gu.double()[:, :301], gu.double()[:, 301:]
+    want = g / (1 + torch.exp(-g)) * u
+    assert torch.allclose(got.double(), want, atol=2 * _eps(dt), rtol=2 * _eps(dt))
+    x = _rand((1000,), torch.float32, 31)
+    assert torch.equal(_ops().cast(x.to(DEV), torch.bfloat16).cpu(), x.to(torch.bfloat16))
+    assert torch.equal(_ops().cast(x.to(torch.bfloat16).to(DEV), torch.float32).cpu(),
+                       x.to(torch.bfloat16).float())
