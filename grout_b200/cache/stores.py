@@ -9,8 +9,9 @@ zeroed: a sequence's length gates every read.  (The reference keeps one
 src/model.rs:1450-1455.)  A store with a window gives pages back as soon as
 every token in them has left the window of all later queries.
 
-``StateStore``: ``[layers, slots, *shape]`` of fixed-size state, zeroed when a
-slot is opened (the reference's packed backend keeps such state per layer,
+``StateStore``: ``[layers, slots + 1, *shape]`` of fixed-size state, zeroed when a
+slot is opened; the last row belongs to no sequence and is where padding rows
+(slot -1) may be pointed, so that a mixer needs no branch for them (the reference's packed backend keeps such state per layer,
 src/quantized.rs:160-169, 376-410).
 """
 from __future__ import annotations
@@ -41,7 +42,7 @@ class KVLayerView:
 
 @dataclass
 class StateLayerView:
-    state: torch.Tensor          # [slots, *shape]
+    state: torch.Tensor          # [slots + 1, *shape]; the last row is for padding rows
     spec: StateSpec
 
 
@@ -136,8 +137,8 @@ class StateStore:
         self.state = None
         self.open_slots = set()
         if allocate:
-            self.state = torch.zeros((n_layers, max_slots) + tuple(spec.shape), dtype=spec.dtype,
-                                     device=self.device)
+            self.state = torch.zeros((n_layers, max_slots + 1) + tuple(spec.shape),
+                                     dtype=spec.dtype, device=self.device)
 
     def open(self, slot: int) -> None:
         if slot in self.open_slots:

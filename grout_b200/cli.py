@@ -1,0 +1,124 @@
+"""Command line in the manner of the reference's ``grout`` binary
+(src/main.rs:13-65 for the options, 96-153 for what is printed) with the
+timing options of its bench binary (benchmarks/src/bin/grout_bench.rs:49-94).
+
+    python -m grout_b200 --model DIR --prompt "Hello" --max-new-tokens 64
+    python -m grout_b200 --model DIR --prompt-ids 1,2,3 --sample --temperature 0.8 --seed 1
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from typing import List, Optional
+
+IM_START, IM_END = "<|im_start|>", "<|im_end|>"
+
+
+def apply_chat_template(prompt: str) -> str:
+    """The reference's literal ChatML wrapper with an empty thinking block
+    (src/model.rs:2198-2210); a prompt that already holds the start marker is
+    left alone."""
+    if IM_START in prompt:
+        return prompt
+    return (f"{IM_START}user\n{prompt}{IM_END}\n{IM_START}assistant\n"
+            f"<think>\n\n</think>\n\n")
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="grout_b200", description="Qwen3 dense text generation on one B200")
+    ap.add_argument("--model", required=True, help="model folder (config.json, safetensors)")
+    g = ap.add_mutually_exclusive_group(required=True)
+    g.add_argument("--prompt", help="text; needs tokenizer.json in the model folder")
+    g.add_argument("--prompt-ids", help="comma-separated token ids, bypassing the tokenizer")
+    ap.add_argument("--max-new-tokens", type=int, default=128)
+    ap.add_argument("--max-seq-len", type=int, default=None,
+                    help="context limit; default min(4096, max_position_embeddings)")
+    ap.add_argument("--sample", action="store_true", help="sample instead of greedy decoding")
+    ap.add_argument("--temperature", type=float, default=None)
+    ap.add_argument("--top-k", type=int, default=None)
+    ap.add_argument("--top-p", type=float, default=None)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--raw-prompt", action="store_true", help="skip the chat template")
+    ap.add_argument("--device-argmax", action="store_true",
+                    help="choose tokens on the GPU (otherwise logits are copied back and the "
+                         "host chooses)")
+    ap.add_argument("--profile", action="store_true", help="print step counts and device times")
+    ap.add_argument("--warmup-reps", type=int, default=1,
+                    help="discarded generations before the measured one")
+    ap.add_argument("--ignore-eos", action="store_true", help="generate the whole budget")
+    ap.add_argument("--fp32", action="store_true", help="run the true 32-bit path")
+    ap.add_argument("--output-json", default=None, help="write token ids, counts and seconds here")
+    ap.add_argument("--device", default="cuda:0")
+    return ap
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    args = build_parser().parse_args(argv)
+    from .engine import Engine
+    from .engine.profile import StepProfile
+    from .sampling import SamplingParams
+
+    tokenizer = None
+    if args.prompt is not None:
+        path = os.path.join(args.model, "tokenizer.json")
+        if not os.path.exists(path):
+            print(f"error: --prompt needs {path}; use --prompt-ids instead", file=sys.stderr)
+            return 2
+        from tokenizers import Tokenizer
+        tokenizer = Tokenizer.from_file(path)
+        text = args.prompt
+        vocab = tokenizer.get_vocab(True)
+        if not args.raw_prompt and IM_START in vocab and IM_END in vocab:   # src/model.rs:1336-1338
+            text = apply_chat_template(text)
+        prompt_ids = tokenizer.encode(text, add_special_tokens=True).ids
+    else:
+        try:
+            prompt_ids = [int(t) for t in args.prompt_ids.replace(" ", "").split(",") if t != ""]
+        except ValueError:
+            print("error: --prompt-ids takes comma-separated integers", file=sys.stderr)
+            return 2
+
+    engine = Engine.load(args.model, dtype="float32" if args.fp32 else "bfloat16",
+                         device=args.device, max_seq_len=args.max_seq_len, max_batch=1)
+    base = engine.default_sampling(args.sample, args.seed)
+    sampling = SamplingParams(args.sample,
+                              args.temperature if args.temperature is not None else base.temperature,
+                              args.top_k if args.top_k is not None else base.top_k,
+                              args.top_p if args.top_p is not None else base.top_p,
+                              args.seed).normalised()
+    print(f"Loaded model from {args.model}")
+    print(f"Prompt: {args.prompt if args.prompt is not None else prompt_ids}")
+    print(f"Generating {args.max_new_tokens} tokens...")
+
+    def run(n):
+        return engine.generate([prompt_ids], n, sampling=sampling, ignore_eos=args.ignore_eos,
+                               device_argmax=args.device_argmax)[0]
+
+    for _ in range(args.warmup_reps):          # src/main.rs:101-110
+        run(min(args.max_new_tokens, 8))
+    if args.profile:
+        engine.profile = StepProfile()
+    out = run(args.max_new_tokens)
+    text = tokenizer.decode(out.token_ids, skip_special_tokens=False) if tokenizer else None
+    print()
+    print(text if text is not None else " ".join(str(t) for t in out.token_ids))
+    print(f"t/s: {out.prompt_tps():.2f} prompt, {out.decode_phase_tps():.2f} decode phase, "
+          f"{out.total_tps():.2f} end-to-end (prompt_tokens={out.prompt_tokens}, "
+          f"generated_tokens={out.generated_tokens}, prompt_s={out.prompt_elapsed:.3f}, "
+          f"decode_s={out.decode_elapsed:.3f}, total_s={out.total_elapsed:.3f})")
+    if args.profile:
+        print()
+        print(engine.profile.report())
+    if args.output_json:
+        with open(args.output_json, "w", encoding="utf-8") as fh:
+            json.dump({"text": text, "token_ids": out.token_ids, "prompt_tokens": out.prompt_tokens,
+                       "generated_tokens": out.generated_tokens, "finish_reason": out.finish_reason,
+                       "total_seconds": out.total_elapsed}, fh, indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -25,9 +25,12 @@ from ..config import GenerationConfig, load_config, resolve_architecture
 from ..kernels import build as kernel_build
 from ..parts.base import BuildContext
 from ..weights import DictSource, FolderSource, load_params, random_tensor
+from ..sampling import DeviceSampler, HostSampler, SamplingParams
 from .batch import make_context
+from .generate import GenerationLoop, GenerationOutput, Request
 from .graphs import DecodeGraphs
 from .model import Model
+from .profile import StepProfile
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
            "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -68,6 +71,10 @@ class Engine:
         self.use_graphs = (dtype == torch.bfloat16) if use_graphs is None else bool(use_graphs)
         self.graphs = DecodeGraphs(model, self.cache, device)
         self.vocab_size = plan.vocab_size
+        self.max_batch = self.cache.max_slots
+        self.profile: Optional[StepProfile] = None
+        self.sampler = DeviceSampler(device)
+        kernel_build.compile_modules(self.sampler.kernel_modules())
 
     # -- construction --------------------------------------------------------
     @classmethod
@@ -165,6 +172,7 @@ class Engine:
         packed = [(slot, self.cache.length[slot], list(toks)) for slot, toks in entries]
         decode = all(len(t) == 1 for _s, t in entries)
         graph = self.graphs.get(len(entries)) if (decode and self.use_graphs) else None
+        started = self.profile.begin() if self.profile else None
         with torch.cuda.device(self.device):
             if graph is not None:
                 all_rows = graph.run(packed)
@@ -180,4 +188,43 @@ class Engine:
                 logits = self.model.forward(ctx, self.cache)
         for slot, toks in entries:
             self.cache.advance(slot, len(toks))
+        if self.profile:
+            self.profile.end("decode" if decode else "prompt", len(entries),
+                             sum(len(t) for _s, t in entries), started)
         return logits
+
+    # -- generation ------------------------------------------------------------
+    def default_stop_ids(self) -> Tuple[int, ...]:
+        """generation_config.json's eos list replaces config.json's eos
+        (src/model.rs:1340-1348)."""
+        if self.generation_config is not None and self.generation_config.eos_token_ids() is not None:
+            return self.generation_config.eos_token_ids()
+        return tuple(self.plan.stop_tokens)
+
+    def default_sampling(self, do_sample: bool = False, seed: Optional[int] = None) -> SamplingParams:
+        return SamplingParams.from_generation_config(self.generation_config, do_sample, seed)
+
+    def generate(self, prompts, max_new_tokens: int = 128, *,
+                 sampling: Optional[SamplingParams] = None, stop_ids=None, ignore_eos: bool = False,
+                 device_argmax: bool = True, include_stop: bool = False) -> List[GenerationOutput]:
+        """prompts: lists of token ids (or ready ``Request`` objects).  Requests
+        are served in batches of unequal prompts; tokens come back as host ints."""
+        sampling = (sampling or SamplingParams()).normalised()
+        if ignore_eos:
+            stops: Tuple[int, ...] = ()               # src/model.rs:1517-1521
+        elif stop_ids is None:
+            stops = self.default_stop_ids()
+        else:
+            stops = tuple(int(t) for t in stop_ids)
+        requests = [p if isinstance(p, Request) else
+                    Request(list(p), max_new_tokens, sampling, stops, include_stop) for p in prompts]
+        sampler = self.sampler if device_argmax else HostSampler()
+
+        def choose(logits, params, draws):
+            out = sampler.choose(logits, params, draws)
+            return out.tolist() if isinstance(out, torch.Tensor) else out
+
+        loop = GenerationLoop(self, choose, max_batch=self.max_batch,
+                              max_tokens=self.cache.max_tokens, max_seq_len=self.max_seq_len,
+                              vocab_size=self.vocab_size, sync=torch.cuda.synchronize)
+        return loop.run(requests)

@@ -31,7 +31,11 @@ class DecodeGraph:
     def __init__(self, model, cache, n_seqs: int, device):
         self.model, self.cache, self.n, self.device = model, cache, n_seqs, device
         off, total = layout_sizes(n_seqs, n_seqs, n_seqs)
-        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        # pinned staging buffers in a ring: a buffer is rewritten only after the
+        # copy that read it has finished, so steps may be queued without a sync
+        self.staging = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(4)]
+        self.copied = [None] * len(self.staging)
+        self.turn = 0
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)
         self.graph = None
         self.logits = None
@@ -42,13 +46,20 @@ class DecodeGraph:
         n_real = len(entries)
         buf, meta = pack_step(entries, [[0]] * n_real, self.n - n_real)
         full_off, total = layout_sizes(self.n, self.n, self.n)
-        out = self.host.numpy()
+        k = self.turn
+        self.turn = (k + 1) % len(self.staging)
+        if self.copied[k] is not None:
+            self.copied[k].synchronize()
+        out = self.staging[k].numpy()
         out[:] = 0
         # want_rows is the last array, so all others sit at the same offsets
         o_want, _ = full_off["want_rows"]
         out[:o_want] = buf[:o_want]
         out[o_want:o_want + self.n] = np.arange(self.n, dtype=np.int32)
-        self.dev.copy_(self.host, non_blocking=True)
+        self.dev.copy_(self.staging[k], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.copied[k] = ev
         return dict(meta, off=full_off, n_want=self.n)
 
     def _capture(self) -> None:

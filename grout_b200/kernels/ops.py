@@ -318,3 +318,31 @@ def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float
     return attn_generic(q, k_pages, v_pages, block_table, token_seq=step.token_seq,
                         token_pos=step.token_pos, slots=step.slots, page=page, scale=scale,
                         window=window)
+
+
+# ---------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """First maximum of every row of 32-bit logits -> int32 [rows]."""
+    _need(logits, "logits", torch.float32, 2)
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    _check(_fn("sample", "gb_argmax_f32", "piipp")(
+        logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
+    """One token per row from temperature / top-k / top-p sampling with the
+    uniform draw ``u[row]``; a temperature <= 1e-5 means argmax."""
+    _need(logits, "logits", torch.float32, 2)
+    n = logits.shape[0]
+    for t, nm, dt in ((temperature, "temperature", torch.float32), (top_k, "top_k", torch.int32),
+                      (top_p, "top_p", torch.float32), (u, "u", torch.float32)):
+        _need(t, nm, dt, 1)
+        if t.shape[0] != n:
+            raise KernelError(f"{nm} has {t.shape[0]} entries for {n} rows")
+    out = torch.empty((n,), dtype=torch.int32, device=logits.device)
+    _check(_fn("sample", "gb_sample_f32", "piipppppp")(
+        logits.data_ptr(), n, logits.shape[1], temperature.data_ptr(), top_k.data_ptr(),
+        top_p.data_ptr(), u.data_ptr(), out.data_ptr(), _stream()), "sample")
+    return out

@@ -53,7 +53,8 @@ class GQAAttention(Mixer):
 
     def __init__(self, ctx: BuildContext, hidden: int, n_heads: int, n_kv_heads: int,
                  head_dim: int, position: PartSpec, qk_norm_eps: Optional[float] = None,
-                 window: Optional[int] = None, scale: Optional[float] = None):
+                 window: Optional[int] = None, scale: Optional[float] = None,
+                 shares_kv: bool = False):
         super().__init__(ctx)
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot share {n_kv_heads} kv heads")
@@ -61,6 +62,10 @@ class GQAAttention(Mixer):
         self.qk_norm_eps = qk_norm_eps
         self.window = window
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.D)
+        # a layer that attends over another layer's keys and values projects
+        # queries only, stores nothing and owns no cache (the schedule says whose
+        # cache it is given)
+        self.shares_kv = bool(shares_kv)
         self.position = build_part("position", position, ctx)
         self.qkv = self.o = None
         self.q_norm_w = self.k_norm_w = None
@@ -70,26 +75,28 @@ class GQAAttention(Mixer):
 
     def param_specs(self):
         H, nq, nkv, D = self.hidden, self.nq, self.nkv, self.D
-        specs = {
-            "q_proj.weight": ParamSpec((nq * D, H)),
-            "k_proj.weight": ParamSpec((nkv * D, H)),
-            "v_proj.weight": ParamSpec((nkv * D, H)),
-            "o_proj.weight": ParamSpec((H, nq * D)),
-        }
+        specs = {"q_proj.weight": ParamSpec((nq * D, H)), "o_proj.weight": ParamSpec((H, nq * D))}
+        if not self.shares_kv:
+            specs["k_proj.weight"] = ParamSpec((nkv * D, H))
+            specs["v_proj.weight"] = ParamSpec((nkv * D, H))
         if self.qk_norm_eps is not None:
             specs["q_norm.weight"] = ParamSpec((D,), "vector")
-            specs["k_norm.weight"] = ParamSpec((D,), "vector")
+            if not self.shares_kv:
+                specs["k_norm.weight"] = ParamSpec((D,), "vector")
         return specs
 
     def load(self, params):
-        ws = [params["q_proj.weight"], params["k_proj.weight"], params["v_proj.weight"]]
+        ws = [params["q_proj.weight"]]
+        if not self.shares_kv:
+            ws += [params["k_proj.weight"], params["v_proj.weight"]]
         if len({w.dtype for w in ws}) != 1:
             raise ValueError("q, k and v projections must be stored in one dtype to be fused")
-        self.qkv = Linear(torch.cat(ws, dim=0))
+        self.qkv = Linear(torch.cat(ws, dim=0) if len(ws) > 1 else ws[0])
         self.o = Linear(params["o_proj.weight"])
         if self.qk_norm_eps is not None:
             self.q_norm_w = params["q_norm.weight"].contiguous()
-            self.k_norm_w = params["k_norm.weight"].contiguous()
+            if not self.shares_kv:
+                self.k_norm_w = params["k_norm.weight"].contiguous()
 
     def kernel_modules(self):
         mods = ("qk_prepare", "attn_generic") + self.qkv.kernel_modules() + self.o.kernel_modules()
@@ -98,12 +105,26 @@ class GQAAttention(Mixer):
         return mods
 
     def cache_spec(self):
-        return KVSpec(self.nkv, self.D, self.window)
+        return None if self.shares_kv else KVSpec(self.nkv, self.D, self.window)
 
     def forward(self, x, step, cache):
         T = x.shape[0]
         qkv = self.qkv(x)
         rot = self.position.rotary()
+        if cache is None or (cache.spec.n_kv_heads, cache.spec.head_dim) != (self.nkv, self.D):
+            raise ValueError(f"attention with {self.nkv} kv heads of {self.D} was given the cache "
+                             f"{None if cache is None else cache.spec}")
+        if self.shares_kv:
+            q, _ = ops.qk_prepare(qkv, self.nq, 0, self.D, q_w=self.q_norm_w,
+                                  eps=self.qk_norm_eps or 0.0,
+                                  inv_freq=rot.inv_freq if rot else None,
+                                  rot_dim=rot.rot_dim if rot else 0, token_seq=step.token_seq,
+                                  token_pos=step.token_pos, slots=step.slots)
+            if rot is None:
+                q, _k = self.position.apply_qk(q, q[:, :0], step.token_pos)
+            attn = ops.attention(q.contiguous(), cache.k_pages, cache.v_pages, cache.block_table,
+                                 step=step, page=cache.page, scale=self.scale, window=self.window)
+            return self.o(attn.view(T, self.nq * self.D))
         fused = rot is not None or type(self.position).apply_qk is PositionEncoding.apply_qk
         common = dict(q_w=self.q_norm_w, k_w=self.k_norm_w, eps=self.qk_norm_eps or 0.0,
                       token_seq=step.token_seq, token_pos=step.token_pos, slots=step.slots)

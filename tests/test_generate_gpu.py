@@ -1,0 +1,120 @@
+"""Generation through the Python entry point and the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from conftest import ROOT, TINY, random_tokens
+from plain import qwen3 as plain
+from plain import sampling as plain_sampling
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(model_dirs, name, dtype, **kw):
+    from grout_b200.engine import Engine
+    return Engine.load(model_dirs[name], dtype=dtype, max_tokens=2048, max_batch=4, **kw)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_matches_plain_in_32_bit(model_dirs, plain_weights, name):
+    cfg, w = plain_weights[name]
+    eng = _engine(model_dirs, name, "float32")
+    lens = [5, 11, 17] if name == "A" else [1, 7, 30, 64]
+    n_new = 8 if name == "A" else 16
+    prompts = [random_tokens(n, cfg["vocab_size"], 700 + i) for i, n in enumerate(lens)]
+    free = [plain.greedy_generate(w, cfg, p, n_new) for p in prompts]
+    outs = eng.generate(prompts, n_new, ignore_eos=True)
+    assert [o.token_ids for o in outs] == free
+    assert all(o.finish_reason == "length" and o.generated_tokens == n_new for o in outs)
+    # a stop token: the third token of the first request ends it, the others go on
+    stop = free[0][2]
+    want = [plain.greedy_generate(w, cfg, p, n_new, stop_ids=(stop,)) for p in prompts]
+    outs = eng.generate(prompts, n_new, stop_ids=[stop])
+    assert [o.token_ids for o in outs] == want
+    assert outs[0].finish_reason == "stop" and len(outs[0].token_ids) <= 2
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0 and eng.cache.tokens_held() == 0
+
+
+def test_more_requests_than_slots_are_served_batch_after_batch(model_dirs, plain_weights):
+    cfg, w = plain_weights["A"]
+    eng = _engine(model_dirs, "A", "float32")
+    prompts = [random_tokens(3 + 2 * i, 256, 720 + i) for i in range(9)]    # 9 requests, 4 slots
+    outs = eng.generate(prompts, 5, ignore_eos=True)
+    assert [o.token_ids for o in outs] == [plain.greedy_generate(w, cfg, p, 5) for p in prompts]
+    assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("device_argmax", [True, False])
+def test_bf16_greedy_choices_are_the_plain_best_within_rounding(model_dirs, plain_weights,
+                                                                device_argmax):
+    cfg, w = plain_weights["B"]
+    eng = _engine(model_dirs, "B", "bfloat16")
+    prompts = [random_tokens(n, 384, 740 + n) for n in (3, 40, 70)]
+    outs = eng.generate(prompts, 12, ignore_eos=True, device_argmax=device_argmax)
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o.token_ids:
+            row = plain.logits(w, cfg, seq, rows=[len(seq) - 1])[0]
+            assert float(row[tok]) >= float(row.max()) - 0.03
+            seq.append(tok)
+
+
+def test_sampled_generation_is_repeatable_and_follows_the_plain_sampler(model_dirs, plain_weights):
+    from grout_b200.sampling import DrawStream, SamplingParams
+    cfg, w = plain_weights["B"]
+    eng = _engine(model_dirs, "B", "float32")
+    prompts = [random_tokens(n, 384, 760 + n) for n in (1, 7, 30, 64)]
+    sp = SamplingParams(True, 0.8, 0, 1.0, seed=11)
+    a = eng.generate(prompts, 16, sampling=sp, ignore_eos=True)
+    b = eng.generate(prompts, 16, sampling=sp, ignore_eos=True)
+    assert [o.token_ids for o in a] == [o.token_ids for o in b]
+    c = eng.generate(prompts, 16, sampling=SamplingParams(True, 0.8, 0, 1.0, seed=12), ignore_eos=True)
+    assert [o.token_ids for o in a] != [o.token_ids for o in c]
+    for i, (p, o) in enumerate(zip(prompts, a)):
+        draws, seq = DrawStream(11, i), list(p)
+        for tok in o.token_ids:
+            row = plain.logits(w, cfg, seq, rows=[len(seq) - 1])[0]
+            assert plain_sampling.sample_next(row.tolist(), 0.8, 0, 1.0, draws.next()) == tok
+            seq.append(tok)
+    # top-k and top-p through the same entry point
+    sp2 = SamplingParams(True, 0.9, 5, 0.8, seed=3)
+    for o, p in zip(eng.generate(prompts[:2], 6, sampling=sp2, ignore_eos=True), prompts):
+        draws, seq = DrawStream(3, prompts.index(p)), list(p)
+        for tok in o.token_ids:
+            row = plain.logits(w, cfg, seq, rows=[len(seq) - 1])[0]
+            assert plain_sampling.sample_next(row.tolist(), 0.9, 5, 0.8, draws.next()) == tok
+            seq.append(tok)
+
+
+def test_limits(model_dirs):
+    eng = _engine(model_dirs, "A", "float32")
+    with pytest.raises(ValueError, match="max_seq_len"):
+        eng.generate([[1] * 100], 100)
+    with pytest.raises(ValueError, match="no tokens"):
+        eng.generate([[]], 4)
+    assert eng.generate([[1, 2]], 0)[0].token_ids == []
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.step([(eng.open_sequence(), [256])])
+
+
+def test_command_line(model_dirs, plain_weights, tmp_path):
+    cfg, w = plain_weights["A"]
+    prompt = random_tokens(9, 256, 780)
+    out = str(tmp_path / "out.json")
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    for extra in (["--fp32"], ["--fp32", "--device-argmax", "--profile"]):
+        r = subprocess.run([sys.executable, "-m", "grout_b200", "--model", model_dirs["A"],
+                            "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6",
+                            "--ignore-eos", "--output-json", out] + extra,
+                           capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert "t/s:" in r.stdout and "Generating 6 tokens" in r.stdout
+        rec = json.load(open(out))
+        assert rec["token_ids"] == plain.greedy_generate(w, cfg, prompt, 6)
+        assert rec["generated_tokens"] == 6 and rec["prompt_tokens"] == 9
+    assert "profile:" in r.stdout

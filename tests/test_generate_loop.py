@@ -1,0 +1,150 @@
+"""The generation loop's decisions with a scripted stand-in for the model (no GPU)."""
+import pytest
+
+from grout_b200.cache import PAGE_TOKENS
+from grout_b200.engine.generate import GenerationLoop, Request, plan_batches
+from grout_b200.sampling import SamplingParams
+
+
+class Script:
+    """Stands in for the engine: request r's n-th generated token is script[r][n];
+    a step returns, per row, which request it belongs to and how long it is now."""
+
+    def __init__(self, prompts, script, max_slots=4):
+        self.prompts, self.script = prompts, script
+        self.by_prompt = {tuple(p): i for i, p in enumerate(prompts)}
+        self.free = list(range(max_slots))
+        self.open, self.request_of, self.steps, self.max_live = {}, {}, [], 0
+        self.history = []
+
+    def open_sequence(self):
+        s = self.free.pop()
+        self.open[s] = []
+        self.request_of[s] = None
+        self.history.append(("open", s))
+        return s
+
+    def close_sequence(self, s):
+        assert s in self.open, "closed twice"
+        del self.open[s]
+        self.free.append(s)
+        self.history.append(("close", s))
+
+    def step(self, entries, want):
+        self.max_live = max(self.max_live, len(self.open))
+        rows = []
+        for (slot, toks), w in zip(entries, want):
+            assert slot in self.open
+            self.open[slot].extend(toks)
+            if self.request_of[slot] is None:
+                assert tuple(self.open[slot]) in self.by_prompt, "first step must bring the prompt"
+                self.request_of[slot] = self.by_prompt[tuple(self.open[slot])]
+                assert w == [len(toks) - 1]
+            else:
+                assert len(toks) == 1 and w == [0]
+            rows.append((self.request_of[slot], len(self.open[slot])))
+        self.steps.append([r for r, _ in rows])
+        return rows
+
+    def choose(self, rows, params, draws):
+        return [self.script[r][length - len(self.prompts[r])] for r, length in rows]
+
+
+def _loop(prompts, script, **kw):
+    st = Script(prompts, script, kw.pop("max_slots", 4))
+    loop = GenerationLoop(st, st.choose, max_batch=kw.pop("max_batch", 4),
+                          max_tokens=kw.pop("max_tokens", 4096), max_seq_len=kw.pop("max_seq_len", 512),
+                          vocab_size=1000)
+    return st, loop
+
+
+def test_stop_token_ends_a_request_and_is_not_returned():
+    prompts = [[1, 2, 3], [4, 5]]
+    script = [[10, 11, 99, 12], [20, 21, 22, 23, 24]]
+    st, loop = _loop(prompts, script)
+    outs = loop.run([Request(prompts[0], 8, stop_ids=(99,)), Request(prompts[1], 4, stop_ids=(99,))])
+    assert outs[0].token_ids == [10, 11] and outs[0].finish_reason == "stop"
+    assert outs[1].token_ids == [20, 21, 22, 23] and outs[1].finish_reason == "length"
+    # the shorter request left the batch: later steps carry request 1 alone
+    assert st.steps == [[0, 1], [0, 1], [0, 1], [1]]
+    assert not st.open and sorted(st.free) == [0, 1, 2, 3]
+    # no step after the last token: 1 prompt step + 3 decode steps for 4 tokens
+    assert loop.steps_run == 4
+
+
+def test_stop_token_can_be_returned_on_request():
+    st, loop = _loop([[1]], [[5, 99]])
+    out = loop.run([Request([1], 8, stop_ids=(99,), include_stop=True)])[0]
+    assert out.token_ids == [5, 99] and out.finish_reason == "stop"
+
+
+def test_first_token_may_already_stop():
+    st, loop = _loop([[1, 2]], [[99]])
+    out = loop.run([Request([1, 2], 8, stop_ids=(99,))])[0]
+    assert out.token_ids == [] and out.generated_tokens == 0 and loop.steps_run == 1
+
+
+def test_zero_budget_runs_nothing():
+    st, loop = _loop([[1, 2]], [[5]])
+    out = loop.run([Request([1, 2], 0)])[0]
+    assert out.token_ids == [] and loop.steps_run == 0 and st.history == []
+
+
+def test_batches_follow_one_another_and_reuse_slots():
+    prompts = [[i + 1] * (i + 1) for i in range(5)]
+    script = [[100 + i] * 3 for i in range(5)]
+    st, loop = _loop(prompts, script, max_batch=2, max_slots=2)
+    outs = loop.run([Request(p, 3) for p in prompts])
+    assert [o.token_ids for o in outs] == script
+    assert st.max_live <= 2
+    opened = [s for what, s in st.history if what == "open"]
+    assert len(opened) == 5 and set(opened) == {0, 1}
+    assert [sorted(s) for s in st.steps if len(s) == 2][0] == [0, 1]
+
+
+def test_token_budget_cuts_batches():
+    reqs = [Request([1] * 10, 50), Request([1] * 70, 60), Request([1] * 5, 5), Request([1], 0)]
+    # rounded to pages: 64, 192, 64
+    assert plan_batches(reqs, 8, 4096) == [[0, 1, 2]]
+    assert plan_batches(reqs, 8, 256) == [[0, 1], [2]]
+    assert plan_batches(reqs, 1, 4096) == [[0], [1], [2]]
+    with pytest.raises(ValueError):
+        plan_batches(reqs, 8, 128)
+    assert PAGE_TOKENS == 64
+
+
+def test_limits_are_checked_before_anything_runs():
+    st, loop = _loop([[1]], [[5]], max_seq_len=16)
+    with pytest.raises(ValueError, match="no tokens"):
+        loop.run([Request([], 4)])
+    with pytest.raises(ValueError, match="max_seq_len"):
+        loop.run([Request([1] * 10, 7)])
+    with pytest.raises(ValueError, match="vocabulary"):
+        loop.run([Request([1000], 2)])
+    assert st.history == []
+
+
+def test_slots_are_given_back_when_a_step_fails():
+    st, loop = _loop([[1, 2]], [[5, 6, 7]])
+    calls = {"n": 0}
+    real = st.step
+
+    def failing(entries, want):
+        calls["n"] += 1
+        if calls["n"] == 2:
+            raise RuntimeError("boom")
+        return real(entries, want)
+    st.step = failing
+    with pytest.raises(RuntimeError):
+        loop.run([Request([1, 2], 3)])
+    assert not st.open
+
+
+def test_draws_are_per_request_and_repeatable():
+    from grout_b200.sampling import DrawStream
+    a = [DrawStream(7, 0).next() for _ in range(1)] + [DrawStream(7, 0).next()]
+    assert a[0] == a[1] and 0.0 <= a[0] < 1.0
+    s1, s2 = DrawStream(7, 0), DrawStream(7, 1)
+    assert [s1.next() for _ in range(3)] != [s2.next() for _ in range(3)]
+    assert SamplingParams(True, 0.0).normalised().temperature == 1e-5
+    assert SamplingParams(False, 0.8).greedy and not SamplingParams(True, 0.8).greedy
