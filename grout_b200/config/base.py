@@ -36,6 +36,8 @@ def _type_ok(value: Any, annot: Any) -> bool:
         return isinstance(value, (list, tuple)) and all(_type_ok(v, inner) for v in value)
     if origin is dict:
         return isinstance(value, dict)
+    if annot in (tuple, list):
+        return isinstance(value, (list, tuple))
     if annot is Any:
         return True
     if annot is type(None):

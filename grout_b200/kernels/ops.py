@@ -306,15 +306,124 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16)
     return y
 
 
+# ---------------------------------------------------------------- fast bf16 attention
+class _PrefillArgs(ctypes.Structure):
+    _fields_ = [("q", _P), ("k_pages", _P), ("v_pages", _P), ("block_table", _P), ("cu_q", _P),
+                ("slots", _P), ("kv_len", _P), ("out", _P), ("n_seqs", _I), ("nq", _I),
+                ("nkv", _I), ("max_pages", _I), ("window", _I), ("n_qblocks", _I),
+                ("scale_log2", _F)]
+
+
+class _DecodeArgs(ctypes.Structure):
+    _fields_ = [("q", _P), ("k_pages", _P), ("v_pages", _P), ("block_table", _P), ("slots", _P),
+                ("kv_len", _P), ("out", _P), ("part_o", _P), ("part_ml", _P), ("n_seqs", _I),
+                ("nq", _I), ("nkv", _I), ("max_pages", _I), ("page", _I), ("window", _I),
+                ("n_splits", _I), ("scale_log2", _F)]
+
+
+_LOG2E = 1.4426950408889634
+PREFILL_ROWS = 64          # query rows per block of the prefill kernel
+FAST_ATTENTION_MODULES: Tuple[str, ...] = ("attn_prefill_bf16", "attn_decode_bf16")
+_SM_COUNT = {}
+
+
+def _sm_count(device) -> int:
+    i = torch.device(device).index or 0
+    if i not in _SM_COUNT:
+        _SM_COUNT[i] = torch.cuda.get_device_properties(i).multi_processor_count
+    return _SM_COUNT[i]
+
+
+def fast_attention_takes(D: int, nq: int, nkv: int, page: int) -> bool:
+    """Shapes the tensor-core kernels accept; others go to the plain kernel."""
+    return D % 16 == 0 and 16 <= D <= 128 and page == 64 and nq % nkv == 0 and nq // nkv <= 16
+
+
+def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens, page: int,
+                      scale: float, window: Optional[int] = None) -> torch.Tensor:
+    """Causal attention of whole prompts (or their continuation) on the tensor
+    cores.  ``q_lens`` are the host's copy of the sequences' row counts; they size
+    the grid."""
+    T, nq, D = q.shape
+    _need(q, "q", torch.bfloat16, 3)
+    _need(k_pages, "k pages", torch.bfloat16, 4)
+    _need(v_pages, "v pages", torch.bfloat16, 4)
+    nkv = k_pages.shape[1]
+    if tuple(k_pages.shape[1:]) != (nkv, page, D) or v_pages.shape != k_pages.shape:
+        raise KernelError(f"pages are {tuple(k_pages.shape)}, expected [*, nkv, {page}, {D}]")
+    for t, nm in ((block_table, "block table"), (cu_q, "cu_q"), (slots, "slots"), (kv_len, "kv_len")):
+        _need(t, nm, torch.int32)
+    if sum(q_lens) != T or len(q_lens) != slots.shape[0]:
+        raise KernelError("q_lens do not describe the step's rows")
+    out = torch.empty_like(q)
+    a = _PrefillArgs()
+    a.q, a.k_pages, a.v_pages, a.block_table = q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr()
+    a.cu_q, a.slots, a.kv_len, a.out = cu_q.data_ptr(), slots.data_ptr(), kv_len.data_ptr(), out.data_ptr()
+    a.n_seqs, a.nq, a.nkv, a.max_pages = len(q_lens), nq, nkv, block_table.shape[1]
+    a.window = int(window or 0)
+    a.n_qblocks = sum((n + PREFILL_ROWS - 1) // PREFILL_ROWS for n in q_lens)
+    a.scale_log2 = float(scale) * _LOG2E
+    _check(_fn("attn_prefill_bf16", "gb_attn_prefill_bf16", "piip")(
+        ctypes.addressof(a), D, page, _stream()), "attn_prefill_bf16")
+    return out
+
+
+def decode_splits(n_seqs: int, nkv: int, max_kv_len: int, device) -> int:
+    """How many ways the keys of a sequence are split so that the grid fills the
+    GPU about twice over; never more splits than 32-key tiles."""
+    want = (2 * _sm_count(device) + n_seqs * nkv - 1) // (n_seqs * nkv)
+    tiles = max(1, (max_kv_len + 31) // 32)
+    return max(1, min(want, tiles, 64))
+
+
+def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: int, scale: float,
+                     max_kv_len: int, window: Optional[int] = None,
+                     n_splits: Optional[int] = None) -> torch.Tensor:
+    """Attention of one new token per sequence over its cached keys (split-K)."""
+    _need(q, "q", torch.bfloat16, 3)
+    B, nq, D = q.shape
+    _need(k_pages, "k pages", torch.bfloat16, 4)
+    _need(v_pages, "v pages", torch.bfloat16, 4)
+    nkv = k_pages.shape[1]
+    if tuple(k_pages.shape[1:]) != (nkv, page, D) or v_pages.shape != k_pages.shape:
+        raise KernelError(f"pages are {tuple(k_pages.shape)}, expected [*, nkv, {page}, {D}]")
+    for t, nm in ((block_table, "block table"), (slots, "slots"), (kv_len, "kv_len")):
+        _need(t, nm, torch.int32)
+    if slots.shape[0] != B or kv_len.shape[0] != B:
+        raise KernelError("one slot and one length per query row are needed")
+    ns = int(n_splits) if n_splits else decode_splits(B, nkv, max_kv_len, q.device)
+    out = torch.empty_like(q)
+    part_o = part_ml = None
+    if ns > 1:
+        part_o = torch.empty((B, nq, ns, D), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((B, nq, ns, 2), dtype=torch.float32, device=q.device)
+    a = _DecodeArgs()
+    a.q, a.k_pages, a.v_pages, a.block_table = q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr()
+    a.slots, a.kv_len, a.out = slots.data_ptr(), kv_len.data_ptr(), out.data_ptr()
+    a.part_o, a.part_ml = _ptr(part_o), _ptr(part_ml)
+    a.n_seqs, a.nq, a.nkv, a.max_pages, a.page = B, nq, nkv, block_table.shape[1], page
+    a.window, a.n_splits, a.scale_log2 = int(window or 0), ns, float(scale) * _LOG2E
+    _check(_fn("attn_decode_bf16", "gb_attn_decode_bf16", "pip")(
+        ctypes.addressof(a), D, _stream()), "attn_decode_bf16")
+    return out
+
+
 # ---------------------------------------------------------------- attention dispatch
-FAST_ATTENTION_MODULES: Tuple[str, ...] = ()
-
-
 def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float,
               window: Optional[int] = None) -> torch.Tensor:
     """Attention of the step's queries over their sequences' cached keys.
-    32-bit tensors take the plain 32-bit kernel; bfloat16 takes the fast kernels
-    where they accept the shape and the plain kernel elsewhere."""
+    32-bit tensors take the plain 32-bit kernel; bfloat16 takes the tensor-core
+    kernels where they accept the shape and the plain kernel elsewhere."""
+    _T, nq, D = q.shape
+    if q.dtype == torch.bfloat16 and fast_attention_takes(D, nq, k_pages.shape[1], page):
+        if step.decode:
+            return attn_decode_bf16(q, k_pages, v_pages, block_table, slots=step.slots,
+                                    kv_len=step.kv_len, page=page, scale=scale,
+                                    max_kv_len=step.max_kv_len, window=window)
+        if step.q_lens:
+            return attn_prefill_bf16(q, k_pages, v_pages, block_table, cu_q=step.cu_q,
+                                     slots=step.slots, kv_len=step.kv_len, q_lens=step.q_lens,
+                                     page=page, scale=scale, window=window)
     return attn_generic(q, k_pages, v_pages, block_table, token_seq=step.token_seq,
                         token_pos=step.token_pos, slots=step.slots, page=page, scale=scale,
                         window=window)

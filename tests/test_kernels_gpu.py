@@ -275,3 +275,97 @@ def test_silu_mul_and_cast(dtype):
     assert torch.equal(_ops().cast(x.to(DEV), torch.bfloat16).cpu(), x.to(torch.bfloat16))
     assert torch.equal(_ops().cast(x.to(torch.bfloat16).to(DEV), torch.float32).cpu(),
                        x.to(torch.bfloat16).float())
+
+
+# ------------------------------------------------------------------ tensor-core attention
+FAST_TOL = dict(atol=6e-3, rtol=1e-2)   # probabilities and outputs are rounded to bf16
+
+
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("nq,nkv,D", [(6, 2, 48), (8, 1, 128), (3, 3, 16), (16, 4, 64)])
+def test_attn_prefill_bf16(nq, nkv, D, window):
+    dt = torch.bfloat16
+    # (tokens already held, tokens of this step): fresh prompts and continued ones
+    plan = [(0, 1), (0, 130), (37, 100), (64, 64), (0, 200), (5, 63)]
+    lens = [s + n for s, n in plan]
+    pc = Paged(lens, nkv, D, dt, 40)
+    q_lens = [n for _, n in plan]
+    T = sum(q_lens)
+    q = _rand((T, nq, D), dt, 41)
+    scale = 1.0 / math.sqrt(D)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    if window is None:
+        # the far key: the last row of the 200-token prompt looks at key 3 only
+        seq, key, row = 4, 3, cu[4] + 199
+        q[row] = 0
+        q[row, :, 0] = 30.0
+        pc.k[seq][:, :, 0] = 0
+        pc.k[seq][key, :, 0] = 30.0
+        for j in range(lens[seq]):
+            pc.store(seq, j, pc.k[seq][j], pc.v[seq][j])
+    got = _ops().attn_prefill_bf16(
+        q.to(DEV), pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV),
+        cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+        slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
+        kv_len=torch.tensor(lens, dtype=torch.int32, device=DEV), q_lens=tuple(q_lens), page=64,
+        scale=scale, window=window).cpu()
+    assert not torch.isnan(got.float()).any()
+    for s, (start, n) in enumerate(plan):
+        for i in ([0, n // 2, n - 1] if n > 2 else range(n)):
+            want = _attn_oracle(q[cu[s] + i], pc.k[s], pc.v[s], start + i, scale, window)
+            assert torch.allclose(got[cu[s] + i].double(), want, **FAST_TOL), (s, i)
+    # every row of one long sequence
+    s, (start, n) = 2, plan[2]
+    for i in range(n):
+        want = _attn_oracle(q[cu[s] + i], pc.k[s], pc.v[s], start + i, scale, window)
+        assert torch.allclose(got[cu[s] + i].double(), want, **FAST_TOL), (s, i)
+    if window is None:
+        assert torch.allclose(got[cu[4] + 199, 0].double(), pc.v[4][3, 0].double(), atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("n_splits", [1, 3, None])
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("nq,nkv,D", [(6, 2, 48), (8, 1, 128), (3, 3, 16), (32, 8, 128), (16, 1, 32)])
+def test_attn_decode_bf16(nq, nkv, D, window, n_splits):
+    dt = torch.bfloat16
+    lens = [1, 130, 200, 64, 33, 65]
+    pc = Paged(lens, nkv, D, dt, 42)
+    B = len(lens) + 1                               # one padding row at the end
+    q = _rand((B, nq, D), dt, 43)
+    scale = 1.0 / math.sqrt(D)
+    if window is None:
+        q[2] = 0
+        q[2, :, 0] = 30.0
+        pc.k[2][:, :, 0] = 0
+        pc.k[2][5, :, 0] = 30.0
+        for j in range(lens[2]):
+            pc.store(2, j, pc.k[2][j], pc.v[2][j])
+    got = _ops().attn_decode_bf16(
+        q.to(DEV), pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV),
+        slots=torch.tensor(pc.slot_of + [-1], dtype=torch.int32, device=DEV),
+        kv_len=torch.tensor(lens + [7], dtype=torch.int32, device=DEV), page=64, scale=scale,
+        max_kv_len=256, window=window, n_splits=n_splits).cpu()
+    assert not torch.isnan(got.float()).any()
+    for s, n in enumerate(lens):
+        want = _attn_oracle(q[s], pc.k[s], pc.v[s], n - 1, scale, window)
+        assert torch.allclose(got[s].double(), want, **FAST_TOL), (s, n)
+    assert bool((got[B - 1] == 0).all())            # the padding row
+    if window is None:
+        assert torch.allclose(got[2, 0].double(), pc.v[2][5, 0].double(), atol=1e-2, rtol=1e-2)
+
+
+def test_fast_attention_refuses_what_it_cannot_do():
+    ops = _ops()
+    assert ops.fast_attention_takes(128, 32, 8, 64)
+    assert not ops.fast_attention_takes(40, 4, 2, 64)       # head size not in steps of 16
+    assert not ops.fast_attention_takes(256, 4, 2, 64)
+    assert not ops.fast_attention_takes(64, 34, 2, 64)      # 17 heads per group
+    pc = Paged([5], 2, 40, torch.bfloat16, 44)
+    q = _rand((1, 4, 40), torch.bfloat16, 45).to(DEV)
+    with pytest.raises(ops.KernelError):
+        ops.attn_decode_bf16(q, pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV),
+                             slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
+                             kv_len=torch.tensor([5], dtype=torch.int32, device=DEV), page=64,
+                             scale=1.0, max_kv_len=64)
