@@ -1,0 +1,240 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Qwen3-4B layer sizes with
+random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W]
+
+A "step" is one decode step of the whole batch (default 8 sequences that each
+hold a 2,048-token prompt, context 4096).  ``value`` is decoded tokens per
+second timed on the device with CUDA events over exactly K steps; ``e2e`` is
+the same through ``Engine.generate`` with host token lists in and out.  The
+line also carries the 2,048-token prefill, the decode step's HBM roofline and
+decode at batch 1 and 64.  Every decode step reads the 8 GB of weights, far more
+than the 126 MB L2, so nothing is flushed between timed steps.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_4B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=151936,
+                hidden_size=2560, intermediate_size=9728, num_hidden_layers=36,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=1000000.0,
+                rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=True,
+                use_sliding_window=False, eos_token_id=151645)
+FULL_LAYERS = 36
+CONTEXT = 4096
+PROMPT = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as fh:
+                p = json.load(fh)
+            return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                    "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons every 200 ms while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6
+                          for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons}
+
+
+def weight_bytes(cfg, layers):
+    H, D = cfg["hidden_size"], cfg["head_dim"]
+    nq, nkv, I, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"], cfg["vocab_size"]
+    per_layer = (nq + 2 * nkv) * D * H + nq * D * H + 3 * H * I + 2 * H + 2 * D
+    return 2 * (layers * per_layer + V * H + H)          # bf16; the head reads the table once
+
+
+def kv_bytes_per_token(cfg, layers):
+    return layers * 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def prefill_flops(cfg, layers, T):
+    H, D = cfg["hidden_size"], cfg["head_dim"]
+    nq, nkv, I, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["intermediate_size"], cfg["vocab_size"]
+    linear = 2 * T * ((nq + 2 * nkv) * D * H + nq * D * H + 3 * H * I)
+    attn = 2 * 2 * nq * D * T * (T + 1) // 2
+    return layers * (linear + attn) + 2 * V * H
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
+                    help="fewer layers than the configuration's 36 (both numbers are reported)")
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "NikVisel/grout is a Rust crate (Cargo.toml, no Python packaging); pip "
+                          "cannot install it offline and no Rust toolchain or crates are present"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    W = max(args.warmup, 3)
+    K = args.steps
+
+    import torch
+    from grout_b200.engine import Engine
+    from grout_b200.kernels import ops
+
+    cfg = dict(QWEN3_4B, num_hidden_layers=args.layers)
+    pk = peaks()
+    torch.manual_seed(0)
+    biggest = max(args.batch, 1 if args.no_points else 64)
+    room = PROMPT + W + K + 64
+    eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=biggest * ((room + 63) // 64 * 64),
+                        max_batch=biggest, max_seq_len=CONTEXT)
+    g = torch.Generator().manual_seed(1)
+    V = cfg["vocab_size"]
+
+    def prompt():
+        return torch.randint(0, V, (PROMPT,), generator=g).tolist()
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    # ---- prefill of 2,048 tokens ---------------------------------------------------
+    p = prompt()
+    times = []
+    for i in range(6):
+        s = eng.open_sequence()
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        eng.step([(s, p)], [[PROMPT - 1]])
+        b.record()
+        torch.cuda.synchronize()
+        eng.close_sequence(s)
+        if i >= 2:
+            times.append(a.elapsed_time(b))
+    pre_ms = statistics.median(times)
+    pre_flops = prefill_flops(cfg, args.layers, PROMPT)
+    prefill = {"value": round(PROMPT / pre_ms * 1e3, 1), "tokens": PROMPT, "ms": round(pre_ms, 3),
+               "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode --------------------------------------------------------------------
+    def decode_run(batch, steps, warm, sample_clocks=False):
+        slots = [eng.open_sequence() for _ in range(batch)]
+        for i in range(0, batch, 8):                       # prompts go in, eight at a time
+            eng.step([(s, prompt()) for s in slots[i:i + 8]])
+        toks = torch.randint(0, V, (warm + steps, batch), generator=g).tolist()
+        for i in range(warm):
+            ops.argmax(eng.step([(s, [toks[i][j]]) for j, s in enumerate(slots)], [[0]] * batch))
+        torch.cuda.synchronize()
+        clocks = ClockSampler() if sample_clocks else None
+        if clocks:
+            clocks.start()
+        before = ops.launch_count()
+        a, b = ev(), ev()
+        a.record()
+        for i in range(warm, warm + steps):
+            ops.argmax(eng.step([(s, [toks[i][j]]) for j, s in enumerate(slots)], [[0]] * batch))
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b)
+        launches = ops.launch_count() - before
+        graph = eng.graphs.get(batch)
+        if graph is not None and graph.graph is not None:
+            launches += steps * graph.kernels_per_replay
+        ctx_mid = PROMPT + warm + steps / 2.0
+        for s in slots:
+            eng.close_sequence(s)
+        return ms, launches, ctx_mid, (clocks.stop() if clocks else None)
+
+    ms, launches, ctx_mid, clocks = decode_run(args.batch, K, W, sample_clocks=True)
+    value = args.batch * K / ms * 1e3
+    step_bytes = weight_bytes(cfg, args.layers) + args.batch * ctx_mid * kv_bytes_per_token(cfg, args.layers)
+    achieved = step_bytes / (ms / K * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"]}
+
+    points = {}
+    if not args.no_points:
+        for bsz in (1, 64):
+            m, _l, _c, _ = decode_run(bsz, 32, 4)
+            points[f"decode_b{bsz}"] = round(bsz * 32 / m * 1e3, 1)
+
+    # ---- end to end through the Python entry point -----------------------------------
+    n_new = min(K, 64) + 1
+    prompts = [prompt() for _ in range(args.batch)]
+    eng.generate(prompts, 4, ignore_eos=True)              # warm-up
+    outs = eng.generate(prompts, n_new, ignore_eos=True)
+    e2e_tps = sum(o.generated_tokens - 1 for o in outs) / outs[0].decode_elapsed
+    graph = eng.graphs.get(args.batch)
+    h2d = int(graph.dev.numel() * 4) if graph is not None else 0
+    e2e = {"value": round(e2e_tps, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": 4 * args.batch}
+
+    print(json.dumps({
+        "metric": "decode tok/s (Qwen3-4B shape, batch 8, 2,048-token prompts)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {"model": "Qwen3-4B layer sizes, random weights", "layers": args.layers,
+                   "layers_of_config": FULL_LAYERS, "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+                   "vocab": V, "global_batch": args.batch, "seq_len": CONTEXT,
+                   "prompt_len": PROMPT, "tied_head": True, "parallelism": "single GPU",
+                   "l2": "inputs larger than L2 (8 GB of weights per step), no flush",
+                   "peaks": pk["source"]},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
+        "roofline": roofline, "points": points}))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -39,6 +39,7 @@ class DecodeGraph:
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)
         self.graph = None
         self.logits = None
+        self.kernels_per_replay = 0
 
     def _fill(self, entries) -> dict:
         """Packs the live sequences plus padding rows and copies them to the device.
@@ -75,9 +76,12 @@ class DecodeGraph:
             self.model.forward(step, self.cache)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.current_stream().synchronize()
+        from ..kernels import ops
+        before = ops.launch_count()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             self.logits = self.model.forward(step, self.cache)
+        self.kernels_per_replay = ops.launch_count() - before   # this library's kernels in the graph
         self.graph = g
 
     def run(self, entries) -> torch.Tensor:

@@ -39,8 +39,19 @@ def _fn(mod: str, name: str, sig: str):
     return f
 
 
-def _check(rc: int, what: str) -> None:
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Kernel launches made through this module so far (a decode-attention call
+    with more than one split counts its merge kernel too)."""
+    return _LAUNCHES
+
+
+def _check(rc: int, what: str, kernels: int = 1) -> None:
+    global _LAUNCHES
     if rc == 0:
+        _LAUNCHES += kernels
         return
     if rc in _OWN_ERRORS:
         raise KernelError(f"{what}: {_OWN_ERRORS[rc]}")
@@ -404,7 +415,7 @@ def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: i
     a.n_seqs, a.nq, a.nkv, a.max_pages, a.page = B, nq, nkv, block_table.shape[1], page
     a.window, a.n_splits, a.scale_log2 = int(window or 0), ns, float(scale) * _LOG2E
     _check(_fn("attn_decode_bf16", "gb_attn_decode_bf16", "pip")(
-        ctypes.addressof(a), D, _stream()), "attn_decode_bf16")
+        ctypes.addressof(a), D, _stream()), "attn_decode_bf16", 2 if ns > 1 else 1)
     return out
 
 
