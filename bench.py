@@ -113,6 +113,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS,
                     help="fewer layers than the configuration's 36 (both numbers are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--phases", default="prefill,decode,points,e2e",
+                    help="which measurements to run (a profiler wants one at a time)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -125,6 +127,9 @@ def main() -> int:
         return 2
     W = max(args.warmup, 3)
     K = args.steps
+    phases = set(args.phases.split(","))
+    if args.no_points:
+        phases.discard("points")
 
     import torch
     from grout_b200.engine import Engine
@@ -133,7 +138,7 @@ def main() -> int:
     cfg = dict(QWEN3_4B, num_hidden_layers=args.layers)
     pk = peaks()
     torch.manual_seed(0)
-    biggest = max(args.batch, 1 if args.no_points else 64)
+    biggest = max(args.batch, 64 if "points" in phases else 1)
     room = PROMPT + W + K + 64
     eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=biggest * ((room + 63) // 64 * 64),
                         max_batch=biggest, max_seq_len=CONTEXT)
@@ -149,7 +154,7 @@ def main() -> int:
     # ---- prefill of 2,048 tokens ---------------------------------------------------
     p = prompt()
     times = []
-    for i in range(6):
+    for i in range(6 if "prefill" in phases else 0):
         s = eng.open_sequence()
         torch.cuda.synchronize()
         a, b = ev(), ev()
@@ -160,10 +165,13 @@ def main() -> int:
         eng.close_sequence(s)
         if i >= 2:
             times.append(a.elapsed_time(b))
-    pre_ms = statistics.median(times)
-    pre_flops = prefill_flops(cfg, args.layers, PROMPT)
-    prefill = {"value": round(PROMPT / pre_ms * 1e3, 1), "tokens": PROMPT, "ms": round(pre_ms, 3),
-               "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    prefill = None
+    if times:
+        pre_ms = statistics.median(times)
+        pre_flops = prefill_flops(cfg, args.layers, PROMPT)
+        prefill = {"value": round(PROMPT / pre_ms * 1e3, 1), "tokens": PROMPT, "ms": round(pre_ms, 3),
+                   "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                   "of": pk["source"]}
 
     # ---- decode --------------------------------------------------------------------
     def decode_run(batch, steps, warm, sample_clocks=False):
@@ -202,21 +210,23 @@ def main() -> int:
                 "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"]}
 
     points = {}
-    if not args.no_points:
+    if "points" in phases:
         for bsz in (1, 64):
             m, _l, _c, _ = decode_run(bsz, 32, 4)
             points[f"decode_b{bsz}"] = round(bsz * 32 / m * 1e3, 1)
 
     # ---- end to end through the Python entry point -----------------------------------
-    n_new = min(K, 64) + 1
-    prompts = [prompt() for _ in range(args.batch)]
-    eng.generate(prompts, 4, ignore_eos=True)              # warm-up
-    outs = eng.generate(prompts, n_new, ignore_eos=True)
-    e2e_tps = sum(o.generated_tokens - 1 for o in outs) / outs[0].decode_elapsed
-    graph = eng.graphs.get(args.batch)
-    h2d = int(graph.dev.numel() * 4) if graph is not None else 0
-    e2e = {"value": round(e2e_tps, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": 4 * args.batch}
+    e2e = None
+    if "e2e" in phases:
+        n_new = min(K, 64) + 1
+        prompts = [prompt() for _ in range(args.batch)]
+        eng.generate(prompts, 4, ignore_eos=True)              # warm-up
+        outs = eng.generate(prompts, n_new, ignore_eos=True)
+        e2e_tps = sum(o.generated_tokens - 1 for o in outs) / outs[0].decode_elapsed
+        graph = eng.graphs.get(args.batch)
+        h2d = int(graph.dev.numel() * 4) if graph is not None else 0
+        e2e = {"value": round(e2e_tps, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": 4 * args.batch}
 
     print(json.dumps({
         "metric": "decode tok/s (Qwen3-4B shape, batch 8, 2,048-token prompts)",

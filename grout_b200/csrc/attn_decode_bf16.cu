@@ -2,7 +2,7 @@
 // keys ("split-K") so that a handful of sequences still fills the GPU.
 //
 // Block (split s, kv head, sequence): the G query heads that share the kv head
-// form one 16-row tile (rows >= G are zero); the block's four warps take the
+// form one 16-row tile (rows >= G are zero); the block's two warps take the
 // split's key tiles of 32 keys in turn, each warp streaming its own tiles
 // through its own double-buffered shared memory with asynchronous copies, so no
 // block-wide barrier sits in the key loop.  The warps' (max, sum, accumulator)
@@ -17,7 +17,7 @@
 #include "attn_mma.cuh"
 
 #define DC_BN 32
-#define DC_WARPS 4
+#define DC_WARPS 2
 #define DC_THREADS (DC_WARPS * 32)
 
 struct DecodeArgs {

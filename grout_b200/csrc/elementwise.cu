@@ -2,40 +2,46 @@
 // and conversions between 32-bit and bfloat16.
 #include "common.cuh"
 
-// in [n_rows, 2 I] with the gate in columns [0, I) and up in [I, 2 I);
+// in [n_rows, 2 I]; with group == 0 the gate is in columns [0, I) and up in
+// [I, 2 I); with group g > 0 the columns come in runs of g gates followed by
+// their g ups (the layout the decode product's fused epilogue uses).
 // out[r, i] = g / (1 + exp(-g)) * u in 32-bit, one rounding at the store
 // (the reference's silu_mul_2d_f16, src/kernels.rs:271-296).
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int I) {
+__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int I, int group) {
   const size_t r = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= I) return;
-  const float g = to_f32<T>(in[r * 2 * I + i]);
-  const float u = to_f32<T>(in[r * 2 * I + I + i]);
+  const int gi = group ? (i / group) * 2 * group + (i % group) : i;
+  const int ui = group ? gi + group : I + i;
+  const float g = to_f32<T>(in[r * 2 * I + gi]);
+  const float u = to_f32<T>(in[r * 2 * I + ui]);
   out[r * I + i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
 }
 
 template <typename T>
-static int silu_mul(const void* in, void* out, int n_rows, int I, cudaStream_t s) {
-  if (n_rows < 0 || I <= 0) return GB_ERR_BAD_ARG;
+static int silu_mul(const void* in, void* out, int n_rows, int I, int group, cudaStream_t s) {
+  if (n_rows < 0 || I <= 0 || group < 0 || (group && I % group)) return GB_ERR_BAD_ARG;
   if (n_rows == 0) return 0;
   if (n_rows > 65535) {
     // rows go to grid.y; split very long steps
     for (int r0 = 0; r0 < n_rows; r0 += 65535) {
       const int n = n_rows - r0 < 65535 ? n_rows - r0 : 65535;
-      int e = silu_mul<T>((const T*)in + (size_t)r0 * 2 * I, (T*)out + (size_t)r0 * I, n, I, s);
+      int e = silu_mul<T>((const T*)in + (size_t)r0 * 2 * I, (T*)out + (size_t)r0 * I, n, I, group, s);
       if (e) return e;
     }
     return 0;
   }
-  silu_mul_kernel<T><<<dim3((I + 255) / 256, n_rows), 256, 0, s>>>((const T*)in, (T*)out, I);
+  silu_mul_kernel<T><<<dim3((I + 255) / 256, n_rows), 256, 0, s>>>((const T*)in, (T*)out, I, group);
   return gb_status();
 }
-GB_EXPORT int gb_silu_mul_f32(const void* in, void* out, int n_rows, int I, cudaStream_t s) {
-  return silu_mul<float>(in, out, n_rows, I, s);
+GB_EXPORT int gb_silu_mul_f32(const void* in, void* out, int n_rows, int I, int group,
+                              cudaStream_t s) {
+  return silu_mul<float>(in, out, n_rows, I, group, s);
 }
-GB_EXPORT int gb_silu_mul_bf16(const void* in, void* out, int n_rows, int I, cudaStream_t s) {
-  return silu_mul<bf16>(in, out, n_rows, I, s);
+GB_EXPORT int gb_silu_mul_bf16(const void* in, void* out, int n_rows, int I, int group,
+                               cudaStream_t s) {
+  return silu_mul<bf16>(in, out, n_rows, I, group, s);
 }
 
 template <typename TI, typename TO>

@@ -9,16 +9,30 @@
 //
 // k order inside one MMA is permuted (a lane feeds 8 consecutive k of its row to
 // two MMAs); A and B use the same permutation, so the dot products are exact
-// sums over all k.  The 8 warps of a block split K in interleaved 32-element
-// chunks and are summed in warp order, which fixes the order of every output's
-// sum independently of M.
+// sums over all k.
+//
+// Parallelism.  A block of four warps owns a tile of weight rows and one slice
+// of K; its warps take the slice's 32-element chunks in turn and are summed in
+// warp order.  When N is small the grid is widened by splitting K over
+// `ksplit` blocks per tile so that enough loads are in flight to cover DRAM
+// latency.  Each block then writes its 32-bit partial tile to scratch and bumps
+// the tile's counter; the block that arrives last adds the partials in split
+// order 0..ksplit-1 and writes the output.  No block waits for another, and the
+// order of every sum is fixed by (N, K, M's bucket) alone, never by timing.
+// The counter is left at zero for the next launch.
+//
+// Epilogue variant SILU: the weight rows are gate and up projections interleaved
+// in groups of 8 (rows 16t..16t+7 gate, 16t+8..16t+15 up, for the same 8
+// intermediate features), and the kernel writes silu(gate) * up, N / 2 columns
+// (the reference's silu_mul_2d_f16, src/kernels.rs:271-296, as an epilogue).
 #include "common.cuh"
 
-#define SK_WARPS 8
+#define SK_WARPS 4
+#define SK_THREADS (SK_WARPS * 32)
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
   return v;
@@ -26,22 +40,31 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {
 
 __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
       "{%8,%9}, {%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+struct SkinnyArgs {
+  const bf16* x;       // [M, K]
+  const bf16* W;       // [N, K]
+  void* y;             // [M, N] or, with SILU, [M, N / 2]
+  float* scratch;      // [tiles, ksplit, 8 NT, 16 MT]   (ksplit > 1)
+  unsigned* counters;  // [tiles], zero before the first launch   (ksplit > 1)
+  int M, N, K, ksplit, chunks_per_split;
+};
+
 // NT: activation rows in tiles of 8; MT: weight rows in tiles of 16 per block.
-template <int NT, int MT, typename OutT>
-__global__ void __launch_bounds__(SK_WARPS * 32)
-skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ y, int M,
-              int N, int K) {
+template <int NT, int MT, int UNROLL, typename OutT, bool SILU>
+__global__ void __launch_bounds__(SK_THREADS) skinny_kernel(const SkinnyArgs a) {
   constexpr int ROWS = 16 * MT, COLS = 8 * NT;
   __shared__ float red[COLS][ROWS + 1];
+  __shared__ int is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int r0 = blockIdx.x * ROWS;
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int r0 = tile * ROWS;
+  const int M = a.M, N = a.N, K = a.K;
 
   float acc[MT][NT][4];
 #pragma unroll
@@ -59,7 +82,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __re
     for (int hf = 0; hf < 2; ++hf) {
       const int r = r0 + i * 16 + g + hf * 8;
       wok[i][hf] = r < N;
-      wrow[i][hf] = W + (size_t)(r < N ? r : N - 1) * K;
+      wrow[i][hf] = a.W + (size_t)(r < N ? r : N - 1) * K;
     }
   const bf16* xrow[NT];
   bool xok[NT];
@@ -67,31 +90,42 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __re
   for (int j = 0; j < NT; ++j) {
     const int m = j * 8 + g;
     xok[j] = m < M;
-    xrow[j] = x + (size_t)(m < M ? m : M - 1) * K;
+    xrow[j] = a.x + (size_t)(m < M ? m : M - 1) * K;
   }
 
   const int nchunks = (K + 31) / 32;
-#pragma unroll 4
-  for (int c = warp; c < nchunks; c += SK_WARPS) {
-    const int k = c * 32 + t * 8;
-    const bool kok = k < K;  // K is a multiple of 8, so the 8 elements are all inside
-    uint4 wv[MT][2], xv[NT];
+  const int c_begin = split * a.chunks_per_split;
+  const int c_end = min(nchunks, c_begin + a.chunks_per_split);
+  // UNROLL chunks are fetched before any of them is multiplied, so that a warp
+  // keeps UNROLL * (2 MT + NT) 16-byte loads in flight
+  for (int c = c_begin + warp; c < c_end; c += SK_WARPS * UNROLL) {
+    uint4 wv[UNROLL][MT][2], xv[UNROLL][NT];
 #pragma unroll
-    for (int i = 0; i < MT; ++i)
+    for (int u = 0; u < UNROLL; ++u) {
+      const int cu = c + u * SK_WARPS;
+      const int k = cu * 32 + t * 8;
+      const bool kok = cu < c_end && k < K;  // K is a multiple of 8: all 8 elements are inside
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf)
-        wv[i][hf] = (kok && wok[i][hf]) ? ld_stream(wrow[i][hf] + k) : make_uint4(0, 0, 0, 0);
+      for (int i = 0; i < MT; ++i)
 #pragma unroll
-    for (int j = 0; j < NT; ++j)
-      xv[j] = (kok && xok[j]) ? __ldg(reinterpret_cast<const uint4*>(xrow[j] + k))
-                              : make_uint4(0, 0, 0, 0);
+        for (int hf = 0; hf < 2; ++hf)
+          wv[u][i][hf] = (kok && wok[i][hf]) ? ld_stream(wrow[i][hf] + k) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-    for (int i = 0; i < MT; ++i)
+      for (int j = 0; j < NT; ++j)
+        xv[u][j] = (kok && xok[j]) ? __ldg(reinterpret_cast<const uint4*>(xrow[j] + k))
+                                   : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
-      for (int j = 0; j < NT; ++j) {
-        mma_bf16(acc[i][j], wv[i][0].x, wv[i][1].x, wv[i][0].y, wv[i][1].y, xv[j].x, xv[j].y);
-        mma_bf16(acc[i][j], wv[i][0].z, wv[i][1].z, wv[i][0].w, wv[i][1].w, xv[j].z, xv[j].w);
-      }
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          mma_bf16(acc[i][j], wv[u][i][0].x, wv[u][i][1].x, wv[u][i][0].y, wv[u][i][1].y,
+                   xv[u][j].x, xv[u][j].y);
+          mma_bf16(acc[i][j], wv[u][i][0].z, wv[u][i][1].z, wv[u][i][0].w, wv[u][i][1].w,
+                   xv[u][j].z, xv[u][j].w);
+        }
   }
 
   // sum the warps' partial tiles in warp order
@@ -103,7 +137,7 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __re
         for (int j = 0; j < NT; ++j)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int row = i * 16 + g + (e >> 1) * 8;   // weight row inside the block
+            const int row = i * 16 + g + (e >> 1) * 8;   // weight row inside the tile
             const int col = j * 8 + t * 2 + (e & 1);     // activation row
             if (w == 0) red[col][row] = acc[i][j][e];
             else red[col][row] += acc[i][j][e];
@@ -111,35 +145,83 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __re
     }
     __syncthreads();
   }
-  for (int e = threadIdx.x; e < ROWS * COLS; e += SK_WARPS * 32) {
-    const int row = e % ROWS, col = e / ROWS;
-    if (col < M && r0 + row < N) y[(size_t)col * N + r0 + row] = from_f32<OutT>(red[col][row]);
+
+  if (a.ksplit > 1) {
+    float* mine = a.scratch + ((size_t)tile * a.ksplit + split) * (ROWS * COLS);
+    for (int e = threadIdx.x; e < ROWS * M; e += SK_THREADS) mine[e] = red[e / ROWS][e % ROWS];
+    __threadfence();   // the partial is visible before the counter moves
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned old = atomicAdd(&a.counters[tile], 1u);
+      is_last = (old == (unsigned)a.ksplit - 1u);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();   // see the other blocks' partials
+    const float* all = a.scratch + (size_t)tile * a.ksplit * (ROWS * COLS);
+    for (int e = threadIdx.x; e < ROWS * M; e += SK_THREADS) {
+      float s = 0.f;
+      for (int sp = 0; sp < a.ksplit; ++sp) s += __ldcg(all + (size_t)sp * (ROWS * COLS) + e);
+      red[e / ROWS][e % ROWS] = s;
+    }
+    if (threadIdx.x == 0) a.counters[tile] = 0u;   // ready for the next launch
+    __syncthreads();
+  }
+
+  OutT* y = (OutT*)a.y;
+  if (SILU) {
+    // rows 16q..16q+7 of the tile are gates, 16q+8..16q+15 the matching ups
+    const int n_out = N / 2;
+    for (int e = threadIdx.x; e < (ROWS / 2) * M; e += SK_THREADS) {
+      const int pr = e % (ROWS / 2), col = e / (ROWS / 2);
+      const int row = (pr / 8) * 16 + (pr % 8);
+      const int feat = r0 / 2 + pr;
+      if (feat < n_out) {
+        const float gt = red[col][row], up = red[col][row + 8];
+        y[(size_t)col * n_out + feat] = from_f32<OutT>(gt / (1.0f + expf(-gt)) * up);
+      }
+    }
+  } else {
+    for (int e = threadIdx.x; e < ROWS * M; e += SK_THREADS) {
+      const int row = e % ROWS, col = e / ROWS;
+      if (r0 + row < N) y[(size_t)col * N + r0 + row] = from_f32<OutT>(red[col][row]);
+    }
   }
 }
 
-template <int NT, int MT, typename OutT>
-static int launch(const void* x, const void* W, void* y, int M, int N, int K, cudaStream_t s) {
+template <int NT, int MT, int UNROLL, typename OutT, bool SILU>
+static int launch(const SkinnyArgs& a, cudaStream_t s) {
   const int rows = 16 * MT;
-  skinny_kernel<NT, MT, OutT><<<(N + rows - 1) / rows, SK_WARPS * 32, 0, s>>>(
-      (const bf16*)x, (const bf16*)W, (OutT*)y, M, N, K);
+  dim3 grid((a.N + rows - 1) / rows, a.ksplit);
+  skinny_kernel<NT, MT, UNROLL, OutT, SILU><<<grid, SK_THREADS, 0, s>>>(a);
   return gb_status();
 }
 
-template <typename OutT>
-static int dispatch(const void* x, const void* W, void* y, int M, int N, int K, cudaStream_t s) {
-  if (M <= 8) return launch<1, 1, OutT>(x, W, y, M, N, K, s);
-  if (M <= 16) return launch<2, 1, OutT>(x, W, y, M, N, K, s);
-  if (M <= 32) return launch<4, 2, OutT>(x, W, y, M, N, K, s);
-  return launch<8, 2, OutT>(x, W, y, M, N, K, s);
+template <typename OutT, bool SILU>
+static int dispatch(const SkinnyArgs& a, cudaStream_t s) {
+  if (a.M <= 8) return launch<1, 1, 8, OutT, SILU>(a, s);
+  if (a.M <= 16) return launch<2, 1, 4, OutT, SILU>(a, s);
+  if (a.M <= 32) return launch<4, 2, 2, OutT, SILU>(a, s);
+  return launch<8, 2, 2, OutT, SILU>(a, s);
 }
 
+// Weight rows per tile for M activation rows (the host sizes grid and scratch with it).
+GB_EXPORT int gb_gemm_skinny_tile_rows(int M) { return M <= 16 ? 16 : 32; }
+GB_EXPORT int gb_gemm_skinny_tile_cols(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64)); }
+
 // out_f32: 1 writes 32-bit outputs (logits), 0 writes bf16.
-GB_EXPORT int gb_gemm_skinny_bf16(const void* x, const void* W, void* y, int M, int N, int K,
-                                  int out_f32, cudaStream_t s) {
-  if (M < 0 || N <= 0 || K <= 0) return GB_ERR_BAD_ARG;
-  if (M > 64) return GB_ERR_UNSUPPORTED;
-  if (K % 8) return GB_ERR_UNSUPPORTED;  // rows must start on 16-byte boundaries
-  if ((((uintptr_t)x) | ((uintptr_t)W)) & 15) return GB_ERR_BAD_ARG;
-  if (M == 0) return 0;
-  return out_f32 ? dispatch<float>(x, W, y, M, N, K, s) : dispatch<bf16>(x, W, y, M, N, K, s);
+// silu: 1 for the interleaved gate|up epilogue (then N must be a multiple of 16).
+GB_EXPORT int gb_gemm_skinny_bf16(const SkinnyArgs* a, int out_f32, int silu, cudaStream_t s) {
+  if (a->M < 0 || a->N <= 0 || a->K <= 0 || a->ksplit <= 0 || a->chunks_per_split <= 0)
+    return GB_ERR_BAD_ARG;
+  if (a->M > 64) return GB_ERR_UNSUPPORTED;
+  if (a->K % 8) return GB_ERR_UNSUPPORTED;  // rows must start on 16-byte boundaries
+  if (silu && (a->N % 16)) return GB_ERR_UNSUPPORTED;
+  if ((((uintptr_t)a->x) | ((uintptr_t)a->W)) & 15) return GB_ERR_BAD_ARG;
+  if (a->ksplit > 1 && (!a->scratch || !a->counters)) return GB_ERR_BAD_ARG;
+  if ((long long)a->ksplit * a->chunks_per_split < (a->K + 31) / 32) return GB_ERR_BAD_ARG;
+  if (a->ksplit > 65535) return GB_ERR_BAD_ARG;
+  if (a->M == 0) return 0;
+  if (silu) return out_f32 ? dispatch<float, true>(*a, s) : dispatch<bf16, true>(*a, s);
+  return out_f32 ? dispatch<float, false>(*a, s) : dispatch<bf16, false>(*a, s);
 }

@@ -38,6 +38,79 @@ __global__ void add_rmsnorm_kernel(const float* res_in, const T* __restrict__ de
   }
 }
 
+// The same operation for widths that are a multiple of 4 and at most 16384:
+// every thread keeps its (up to 16) values in registers between the sum of
+// squares and the scaling, and all traffic is in 8- or 16-byte pieces.
+#define NV_MAX 4
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Vec4<bf16> {
+  static __device__ __forceinline__ void load(const bf16* p, float (&v)[4]) {
+    const uint2 x = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&x.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+  }
+  static __device__ __forceinline__ void store(bf16* p, const float (&v)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 x;
+    x.x = *reinterpret_cast<uint32_t*>(&a);
+    x.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = x;
+  }
+};
+
+template <typename T, typename WT>
+__global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* __restrict__ delta,
+                                       const int* __restrict__ rows, const WT* __restrict__ w,
+                                       float eps, float* res_out, T* __restrict__ y, int N) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+  const float* rin = res_in ? res_in + s * N : nullptr;
+  const T* din = delta ? delta + s * N : nullptr;
+  float* rout = res_out ? res_out + (size_t)r * N : nullptr;
+  float v[NV_MAX][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NV_MAX; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < N) {
+      float a[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};
+      if (rin) Vec4<float>::load(rin + i, a);
+      if (din) Vec4<T>::load(din + i, d);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[j][e] = a[e] + d[e];
+        ss += v[j][e] * v[j][e];
+      }
+      if (rout) Vec4<float>::store(rout + i, v[j]);
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)N + eps);
+  T* yo = y + (size_t)r * N;
+#pragma unroll
+  for (int j = 0; j < NV_MAX; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < N) {
+      float wv[4], o[4];
+      Vec4<WT>::load(w + i, wv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[e] = v[j][e] * inv * wv[e];
+      Vec4<T>::store(yo + i, o);
+    }
+  }
+}
+
 static int norm_threads(int N) {
   int t = (N + 3) / 4;
   t = ((t + 31) / 32) * 32;
@@ -53,6 +126,17 @@ static int launch(const float* res_in, const void* delta, const int* rows, const
   // in place is allowed only without a row list (each block then owns its row)
   if (rows && res_out && res_out == res_in) return GB_ERR_BAD_ARG;
   if (n_rows == 0) return 0;
+  const bool aligned = ((((uintptr_t)res_in) | ((uintptr_t)delta) | ((uintptr_t)w) |
+                         ((uintptr_t)res_out) | ((uintptr_t)y)) & 15) == 0;
+  if (N % 4 == 0 && N <= 4 * 1024 * NV_MAX && aligned) {
+    int threads = (N / 4 + NV_MAX - 1) / NV_MAX;      // vectors per thread <= NV_MAX
+    threads = ((threads + 31) / 32) * 32;
+    if (threads < 64) threads = 64;
+    if (threads > 1024) threads = 1024;
+    add_rmsnorm_vec_kernel<T, WT><<<n_rows, threads, 0, stream>>>(
+        res_in, (const T*)delta, rows, (const WT*)w, eps, res_out, (T*)y, N);
+    return gb_status();
+  }
   add_rmsnorm_kernel<T, WT><<<n_rows, norm_threads(N), 0, stream>>>(
       res_in, (const T*)delta, rows, (const WT*)w, eps, res_out, (T*)y, N);
   return gb_status();

@@ -267,15 +267,17 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------- elementwise
-def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+def silu_mul(gate_up: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+    """silu(gate) * up.  ``interleave`` 0: gate in the first half of the columns,
+    up in the second; g > 0: groups of g gate columns followed by their g up columns."""
     _need(gate_up, "gate|up", ndim=2)
     T, two_i = gate_up.shape
-    if two_i % 2:
-        raise KernelError("gate|up must have an even number of columns")
+    if two_i % 2 or (interleave and two_i % (2 * interleave)):
+        raise KernelError("gate|up must have an even number of columns (of whole groups)")
     out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     sfx = _suffix(gate_up.dtype)
-    _check(_fn("elementwise", f"gb_silu_mul_{sfx}", "ppiip")(
-        gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, _stream()), "silu_mul")
+    _check(_fn("elementwise", f"gb_silu_mul_{sfx}", "ppiiip")(
+        gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, int(interleave), _stream()), "silu_mul")
     return out
 
 
@@ -296,8 +298,54 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 SKINNY_MAX_ROWS = 64
 
 
-def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16) -> torch.Tensor:
-    """x [M <= 64, K] . w [N, K]^T, bf16 in, 32-bit accumulate; the decode-time linear."""
+class _SkinnyArgs(ctypes.Structure):
+    _fields_ = [("x", _P), ("W", _P), ("y", _P), ("scratch", _P), ("counters", _P), ("M", _I),
+                ("N", _I), ("K", _I), ("ksplit", _I), ("chunks_per_split", _I)]
+
+
+class _Workspace:
+    """Scratch of the split-K product, one per device: 32-bit partial tiles and
+    one arrival counter per tile.  The counters are zero between launches (the
+    kernel leaves them so).  Launches that share it must be ordered on one
+    stream, which every step of this library is."""
+
+    def __init__(self):
+        self.scratch = None
+        self.counters = None
+        self._kept = []     # outgrown buffers stay alive: captured graphs still point at them
+
+    def get(self, device, n_floats: int, n_counters: int):
+        if self.scratch is None or self.scratch.numel() < n_floats:
+            self._kept.append(self.scratch)
+            self.scratch = torch.empty(max(n_floats, 1 << 22), dtype=torch.float32, device=device)
+        if self.counters is None or self.counters.numel() < n_counters:
+            self._kept.append(self.counters)
+            self.counters = torch.zeros(max(n_counters, 1 << 14), dtype=torch.int32, device=device)
+        return self.scratch, self.counters
+
+
+_WORKSPACES = {}
+
+
+def skinny_split(M: int, N: int, K: int, device) -> Tuple[int, int, int]:
+    """(ksplit, chunks per split, tiles): K is cut over enough blocks that about
+    eight four-warp blocks per SM are resident, as long as every block keeps at
+    least 16 chunks of 32 elements.  It depends on N, K and M's bucket only."""
+    rows = 16 if M <= 16 else 32
+    tiles = (N + rows - 1) // rows
+    nchunks = (K + 31) // 32
+    want = (8 * _sm_count(device) + tiles - 1) // tiles
+    ks = max(1, min(want, nchunks // 16, 16))
+    per = (nchunks + ks - 1) // ks
+    ks = (nchunks + per - 1) // per
+    return ks, per, tiles
+
+
+def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
+                     silu_mul: bool = False) -> torch.Tensor:
+    """x [M <= 64, K] . w [N, K]^T, bf16 in, 32-bit accumulate; the decode-time
+    linear.  With ``silu_mul`` the rows of ``w`` are gate and up rows interleaved
+    in groups of 8 and the result is silu(gate) * up, [M, N / 2]."""
     _need(x, "activations", torch.bfloat16, 2)
     _need(w, "weight", torch.bfloat16, 2)
     M, K = x.shape
@@ -310,10 +358,24 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16)
         raise KernelError(f"gemm_skinny_bf16 needs an inner size that is a multiple of 8, got {K}")
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"output must be bfloat16 or float32, not {out_dtype}")
-    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    _check(_fn("gemm_skinny_bf16", "gb_gemm_skinny_bf16", "pppiiiip")(
-        x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, int(out_dtype == torch.float32),
-        _stream()), "gemm_skinny_bf16")
+    if silu_mul and N % 16:
+        raise KernelError(f"the interleaved gate|up product needs N to be a multiple of 16, got {N}")
+    y = torch.empty((M, N // 2 if silu_mul else N), dtype=out_dtype, device=x.device)
+    if M == 0:
+        return y
+    ks, per, tiles = skinny_split(M, N, K, x.device)
+    a = _SkinnyArgs()
+    a.x, a.W, a.y = x.data_ptr(), w.data_ptr(), y.data_ptr()
+    a.M, a.N, a.K, a.ksplit, a.chunks_per_split = M, N, K, ks, per
+    if ks > 1:
+        rows = 16 if M <= 16 else 32
+        cols = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
+        ws = _WORKSPACES.setdefault(x.device.index or 0, _Workspace())
+        scratch, counters = ws.get(x.device, tiles * ks * rows * cols, tiles)
+        a.scratch, a.counters = scratch.data_ptr(), counters.data_ptr()
+    _check(_fn("gemm_skinny_bf16", "gb_gemm_skinny_bf16", "piip")(
+        ctypes.addressof(a), int(out_dtype == torch.float32), int(silu_mul), _stream()),
+        "gemm_skinny_bf16")
     return y
 
 
@@ -380,11 +442,11 @@ def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, 
 
 
 def decode_splits(n_seqs: int, nkv: int, max_kv_len: int, device) -> int:
-    """How many ways the keys of a sequence are split so that the grid fills the
-    GPU about twice over; never more splits than 32-key tiles."""
-    want = (2 * _sm_count(device) + n_seqs * nkv - 1) // (n_seqs * nkv)
-    tiles = max(1, (max_kv_len + 31) // 32)
-    return max(1, min(want, tiles, 64))
+    """How many ways the keys of a sequence are split: enough blocks for about
+    three waves of three resident blocks per SM, but at least 128 keys a split."""
+    want = (8 * _sm_count(device) + n_seqs * nkv - 1) // (n_seqs * nkv)
+    most = max(1, (max_kv_len + 127) // 128)
+    return max(1, min(want, most, 64))
 
 
 def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: int, scale: float,

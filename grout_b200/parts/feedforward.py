@@ -27,6 +27,7 @@ class SwiGLU(FeedForward):
         super().__init__(ctx)
         self.hidden, self.intermediate = int(hidden), int(intermediate)
         self.gate_up = self.down = None
+        self.interleave = 0
 
     def param_specs(self):
         return {"gate_proj.weight": ParamSpec((self.intermediate, self.hidden)),
@@ -37,11 +38,21 @@ class SwiGLU(FeedForward):
         g, u = params["gate_proj.weight"], params["up_proj.weight"]
         if g.dtype != u.dtype:
             raise ValueError("gate and up projections must be stored in one dtype to be fused")
-        self.gate_up = Linear(torch.cat([g, u], dim=0))
+        # bf16: rows interleaved in groups of 8 (8 gates, their 8 ups, ...) so that
+        # the decode product holds a gate and its up in one tile and can apply
+        # silu(gate) * up before it stores
+        self.interleave = 8 if (g.dtype == torch.bfloat16 and self.intermediate % 8 == 0
+                                and self.hidden % 8 == 0) else 0
+        if self.interleave:
+            k = self.interleave
+            fused = torch.stack([g.view(-1, k, self.hidden), u.view(-1, k, self.hidden)], dim=1)
+            self.gate_up = Linear(fused.reshape(2 * self.intermediate, self.hidden))
+        else:
+            self.gate_up = Linear(torch.cat([g, u], dim=0))
         self.down = Linear(params["down_proj.weight"])
 
     def kernel_modules(self):
         return ("elementwise",) + self.gate_up.kernel_modules() + self.down.kernel_modules()
 
     def forward(self, x, step):
-        return self.down(ops.silu_mul(self.gate_up(x)))
+        return self.down(self.gate_up.silu_mul(x, self.interleave))

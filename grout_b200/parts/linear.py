@@ -47,3 +47,13 @@ class Linear:
         if out_dtype == torch.float32:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
+
+    def silu_mul(self, x: torch.Tensor, interleave: int) -> torch.Tensor:
+        """silu(gate) * up of a fused gate|up weight.  ``interleave`` 0: gate rows
+        first, then up rows; 8: groups of 8 gate rows followed by their 8 up rows,
+        which lets the decode kernel finish the product in its epilogue."""
+        w = self.weight
+        if (interleave == 8 and w.dtype == torch.bfloat16 and x.shape[0] <= ops.SKINNY_MAX_ROWS
+                and self.in_features % 8 == 0):
+            return ops.gemm_skinny_bf16(x, w, x.dtype, silu_mul=True)
+        return ops.silu_mul(self(x), interleave)

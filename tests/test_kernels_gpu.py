@@ -244,6 +244,39 @@ def test_gemm_skinny_bf16(M, N, K, out):
     assert torch.allclose(got.double(), want, atol=2e-5 * math.sqrt(K) + 2 * e, rtol=2 * e)
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 2560, 9728), (3, 160, 4096), (40, 2560, 4096), (16, 6144, 2560)])
+def test_gemm_skinny_split_k(M, N, K):
+    """Shapes whose K is split over several blocks (partials in scratch, the last
+    block sums them); called twice, since the arrival counters must be left at zero."""
+    ops = _ops()
+    assert ops.skinny_split(M, N, K, DEV)[0] > 1
+    x, w = _rand((M, K), torch.bfloat16, 32), _rand((N, K), torch.bfloat16, 33, 0.05)
+    want = x.double() @ w.double().T
+    first = ops.gemm_skinny_bf16(x.to(DEV), w.to(DEV), torch.float32).cpu()
+    second = ops.gemm_skinny_bf16(x.to(DEV), w.to(DEV), torch.float32).cpu()
+    assert torch.equal(first, second)
+    assert torch.allclose(first.double(), want, atol=2e-5 * math.sqrt(K), rtol=1e-5)
+
+
+@pytest.mark.parametrize("M", [1, 8, 11, 33, 64])
+@pytest.mark.parametrize("I,K", [(152, 96), (9728, 2560), (24, 4096)])
+def test_gemm_skinny_silu_epilogue(M, I, K):
+    """Gate and up rows interleaved in groups of 8; the kernel returns silu(gate) * up."""
+    x = _rand((M, K), torch.bfloat16, 34)
+    gate, up = _rand((I, K), torch.bfloat16, 35, 0.05), _rand((I, K), torch.bfloat16, 36, 0.05)
+    w = torch.stack([gate.view(-1, 8, K), up.view(-1, 8, K)], 1).reshape(2 * I, K).contiguous()
+    got = _ops().gemm_skinny_bf16(x.to(DEV), w.to(DEV), torch.bfloat16, silu_mul=True).cpu()
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    want = g / (1 + torch.exp(-g)) * u
+    assert got.shape == (M, I)
+    assert torch.allclose(got.double(), want, atol=2e-4 + 2 * _eps(torch.bfloat16) * 0,
+                          rtol=3 * _eps(torch.bfloat16))
+    # the stand-alone kernel on the same interleaved layout agrees
+    raw = _ops().gemm_skinny_bf16(x.to(DEV), w.to(DEV), torch.float32)
+    two = _ops().silu_mul(raw, 8).cpu()
+    assert torch.allclose(two.double(), want, atol=1e-5, rtol=1e-5)
+
+
 def test_gemm_skinny_row_independent():
     x, w = _rand((16, 512), torch.bfloat16, 26), _rand((300, 512), torch.bfloat16, 27)
     full = _ops().gemm_skinny_bf16(x.to(DEV), w.to(DEV), torch.float32).cpu()
