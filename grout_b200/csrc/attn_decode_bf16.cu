@@ -8,8 +8,10 @@
 // block-wide barrier sits in the key loop.  The warps' (max, sum, accumulator)
 // are merged in shared memory.  With one split the block writes the output;
 // otherwise it writes a 32-bit partial (accumulator relative to its max, max,
-// sum) and gb_attn_decode_merge combines the splits:
-//   out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),  M = max_s m_s.
+// sum) to scratch and bumps the counter of its (sequence, kv head); the block
+// that arrives last combines the splits in split order:
+//   out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),  M = max_s m_s,
+// and leaves the counter at zero.  No block waits for another.
 // The key range of a sequence comes from kv_len on the device, so one captured
 // launch serves every step.  (The reference's pair is fmha_decode_gqa_split +
 // splitk_reduce_merge, src/kernels.rs:2586-2749, 2771-2868, which stores f16
@@ -30,6 +32,7 @@ struct DecodeArgs {
   bf16* out;               // [n_seqs, nq, D]
   float* part_o;           // [n_seqs, nq, n_splits, D]   (n_splits > 1)
   float* part_ml;          // [n_seqs, nq, n_splits, 2]
+  unsigned* counters;      // [n_seqs, nkv], zero before the first launch   (n_splits > 1)
   int n_seqs, nq, nkv, max_pages, page, window, n_splits;
   float scale_log2;
 };
@@ -38,8 +41,11 @@ template <int DT>
 __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArgs a) {
   constexpr int D = 16 * DT, LD = D + 8, CHUNKS = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int is_last;
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);       // [16][LD]
   bf16* kv_s = q_s + 16 * LD;                          // per warp: [2 stages][K, V][32][LD]
+  pdl_launch_dependents();
+  pdl_wait();   // queries and the newest keys are the producer's output
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int G = a.nq / a.nkv;
@@ -56,142 +62,150 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
   const int per_split = (n_tiles + a.n_splits - 1) / a.n_splits;
   const int t_begin = tile_lo + split * per_split;
   const int t_end = min(tile_lo + n_tiles, t_begin + per_split);
+  const bool empty = t_begin >= t_end;   // a padding row, or more splits than tiles
 
-  if (t_begin >= t_end) {  // nothing to do: an empty partial, or zeros for a padding row
+  if (empty) {
     if (single) {
       for (int i = tid; i < G * D; i += DC_THREADS)
         a.out[((size_t)seq * a.nq + h0) * D + i] = __float2bfloat16(0.f);
-    } else {
-      for (int i = tid; i < G; i += DC_THREADS) {
-        float* ml = a.part_ml + (((size_t)seq * a.nq + h0 + i) * a.n_splits + split) * 2;
-        ml[0] = -INFINITY;
-        ml[1] = 0.f;
+      return;
+    }
+    for (int i = tid; i < G; i += DC_THREADS) {
+      float* ml = a.part_ml + (((size_t)seq * a.nq + h0 + i) * a.n_splits + split) * 2;
+      ml[0] = -INFINITY;
+      ml[1] = 0.f;
+    }
+  } else {
+    // the query tile: G rows, the rest zero
+    {
+      const bf16* qsrc = a.q + ((size_t)seq * a.nq + h0) * D;
+      for (int i = tid; i < 16 * CHUNKS; i += DC_THREADS) {
+        const int r = i / CHUNKS, ch = i % CHUNKS;
+        const bool ok = r < G;
+        cp_async16(q_s + r * LD + ch * 8, ok ? qsrc + r * D + ch * 8 : qsrc, ok);
+      }
+      cp_async_commit();
+    }
+    const int* table = a.block_table + (size_t)slot * a.max_pages;
+    bf16* my = kv_s + (size_t)warp * 4 * DC_BN * LD;
+    const int tiles_per_page = a.page / DC_BN;
+
+    auto load_tile = [&](int tile, int stage) {
+      const int page = table[tile / tiles_per_page];
+      const size_t base =
+          (((size_t)page * a.nkv + kvh) * a.page + (tile % tiles_per_page) * DC_BN) * D;
+      bf16* kd = my + (stage * 2 + 0) * DC_BN * LD;
+      bf16* vd = my + (stage * 2 + 1) * DC_BN * LD;
+      const int valid = kv_len - tile * DC_BN;
+      for (int i = lane; i < DC_BN * CHUNKS; i += 32) {
+        const int r = i / CHUNKS, ch = i % CHUNKS;
+        const bool ok = r < valid;
+        cp_async16(kd + r * LD + ch * 8, ok ? a.k_pages + base + r * D + ch * 8 : a.k_pages, ok);
+        cp_async16(vd + r * LD + ch * 8, ok ? a.v_pages + base + r * D + ch * 8 : a.v_pages, ok);
+      }
+    };
+
+    WarpAttn<DT> w;
+    w.init();
+    int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
+    const int first = t_begin + warp;
+    if (first < t_end) load_tile(first, 0);
+    cp_async_commit();
+    cp_async_wait<1>();   // the query tile (older group) has landed for this thread
+    __syncthreads();      // ... and for all threads
+    w.load_q(q_s);
+    int stage = 0;
+    for (int tile = first; tile < t_end; tile += DC_WARPS, stage ^= 1) {
+      if (tile + DC_WARPS < t_end) load_tile(tile + DC_WARPS, stage ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+      __syncwarp();
+      const int key0 = tile * DC_BN;
+      const bf16* kt = my + (stage * 2 + 0) * DC_BN * LD;
+      const bf16* vt = my + (stage * 2 + 1) * DC_BN * LD;
+      if (key0 < key_lo || key0 + DC_BN - 1 > pos)
+        w.template tile<DC_BN, true>(kt, vt, key0, lo, hi, a.scale_log2);
+      else
+        w.template tile<DC_BN, false>(kt, vt, key0, lo, hi, a.scale_log2);
+      __syncwarp();  // all lanes are done with the stage before it is refilled
+    }
+    cp_async_wait<0>();
+    w.finish_l();
+    __syncthreads();  // every warp has left its buffers: reuse them for the merge
+
+    // merge the warps: per warp m[16], l[16], o[16][D] in shared memory
+    float* red = reinterpret_cast<float*>(kv_s);
+    float* red_m = red;                               // [warps][16]
+    float* red_l = red + DC_WARPS * 16;               // [warps][16]
+    float* red_o = red + 2 * DC_WARPS * 16;           // [warps][16][D]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = g + r * 8;
+      if (t == 0) {
+        red_m[warp * 16 + row] = w.m[r];
+        red_l[warp * 16 + row] = w.l[r];
+      }
+#pragma unroll
+      for (int i = 0; i < 2 * DT; ++i) {
+        red_o[((size_t)warp * 16 + row) * D + i * 8 + t * 2] = w.o[i][2 * r];
+        red_o[((size_t)warp * 16 + row) * D + i * 8 + t * 2 + 1] = w.o[i][2 * r + 1];
       }
     }
-    return;
-  }
-
-  // the query tile: G rows, the rest zero
-  {
-    const bf16* qsrc = a.q + ((size_t)seq * a.nq + h0) * D;
-    for (int i = tid; i < 16 * CHUNKS; i += DC_THREADS) {
-      const int r = i / CHUNKS, ch = i % CHUNKS;
-      const bool ok = r < G;
-      cp_async16(q_s + r * LD + ch * 8, ok ? qsrc + r * D + ch * 8 : qsrc, ok);
-    }
-    cp_async_commit();
-  }
-  const int* table = a.block_table + (size_t)slot * a.max_pages;
-  bf16* my = kv_s + (size_t)warp * 4 * DC_BN * LD;
-  const int tiles_per_page = a.page / DC_BN;
-
-  auto load_tile = [&](int tile, int stage) {
-    const int page = table[tile / tiles_per_page];
-    const size_t base = (((size_t)page * a.nkv + kvh) * a.page + (tile % tiles_per_page) * DC_BN) * D;
-    bf16* kd = my + (stage * 2 + 0) * DC_BN * LD;
-    bf16* vd = my + (stage * 2 + 1) * DC_BN * LD;
-    const int valid = kv_len - tile * DC_BN;
-    for (int i = lane; i < DC_BN * CHUNKS; i += 32) {
-      const int r = i / CHUNKS, ch = i % CHUNKS;
-      const bool ok = r < valid;
-      cp_async16(kd + r * LD + ch * 8, ok ? a.k_pages + base + r * D + ch * 8 : a.k_pages, ok);
-      cp_async16(vd + r * LD + ch * 8, ok ? a.v_pages + base + r * D + ch * 8 : a.v_pages, ok);
-    }
-  };
-
-  WarpAttn<DT> w;
-  w.init();
-  int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
-  const int first = t_begin + warp;
-  if (first < t_end) load_tile(first, 0);
-  cp_async_commit();
-  cp_async_wait<1>();   // the query tile (older group) has landed for this thread
-  __syncthreads();      // ... and for all threads
-  w.load_q(q_s);
-  int stage = 0;
-  for (int tile = first; tile < t_end; tile += DC_WARPS, stage ^= 1) {
-    if (tile + DC_WARPS < t_end) load_tile(tile + DC_WARPS, stage ^ 1);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncwarp();
-    const int key0 = tile * DC_BN;
-    const bf16* kt = my + (stage * 2 + 0) * DC_BN * LD;
-    const bf16* vt = my + (stage * 2 + 1) * DC_BN * LD;
-    if (key0 < key_lo || key0 + DC_BN - 1 > pos)
-      w.template tile<DC_BN, true>(kt, vt, key0, lo, hi, a.scale_log2);
-    else
-      w.template tile<DC_BN, false>(kt, vt, key0, lo, hi, a.scale_log2);
-    __syncwarp();  // all lanes are done with the stage before it is refilled
-  }
-  cp_async_wait<0>();
-  w.finish_l();
-  __syncthreads();  // every warp has left its buffers: reuse them for the merge
-
-  // merge the warps: per warp m[16], l[16], o[16][D] in shared memory
-  float* red = reinterpret_cast<float*>(kv_s);
-  float* red_m = red;                               // [warps][16]
-  float* red_l = red + DC_WARPS * 16;               // [warps][16]
-  float* red_o = red + 2 * DC_WARPS * 16;           // [warps][16][D]
+    __syncthreads();
+    for (int i = tid; i < G * D; i += DC_THREADS) {
+      const int row = i / D, d = i % D;
+      float M = -INFINITY;
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int row = g + r * 8;
-    if (t == 0) {
-      red_m[warp * 16 + row] = w.m[r];
-      red_l[warp * 16 + row] = w.l[r];
-    }
+      for (int wi = 0; wi < DC_WARPS; ++wi) M = fmaxf(M, red_m[wi * 16 + row]);
+      float L = 0.f, O = 0.f;
 #pragma unroll
-    for (int i = 0; i < 2 * DT; ++i) {
-      red_o[((size_t)warp * 16 + row) * D + i * 8 + t * 2] = w.o[i][2 * r];
-      red_o[((size_t)warp * 16 + row) * D + i * 8 + t * 2 + 1] = w.o[i][2 * r + 1];
+      for (int wi = 0; wi < DC_WARPS; ++wi) {
+        const float mw = red_m[wi * 16 + row];
+        const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+        L += red_l[wi * 16 + row] * f;
+        O += red_o[((size_t)wi * 16 + row) * D + d] * f;
+      }
+      if (single) {
+        a.out[((size_t)seq * a.nq + h0 + row) * D + d] = __float2bfloat16(O / L);
+      } else {
+        const size_t p = ((size_t)seq * a.nq + h0 + row) * a.n_splits + split;
+        a.part_o[p * D + d] = O;
+        if (d == 0) {
+          a.part_ml[p * 2] = M;
+          a.part_ml[p * 2 + 1] = L;
+        }
+      }
     }
+  }
+  if (single) return;
+
+  // the block that arrives last combines the splits of its (sequence, kv head)
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned old = atomicAdd(&a.counters[seq * a.nkv + kvh], 1u);
+    is_last = (old == (unsigned)a.n_splits - 1u);
   }
   __syncthreads();
+  if (!is_last) return;
+  __threadfence();
   for (int i = tid; i < G * D; i += DC_THREADS) {
     const int row = i / D, d = i % D;
+    const size_t p0 = ((size_t)seq * a.nq + h0 + row) * a.n_splits;
     float M = -INFINITY;
-#pragma unroll
-    for (int wi = 0; wi < DC_WARPS; ++wi) M = fmaxf(M, red_m[wi * 16 + row]);
+    for (int sp = 0; sp < a.n_splits; ++sp) M = fmaxf(M, __ldcg(a.part_ml + (p0 + sp) * 2));
     float L = 0.f, O = 0.f;
-#pragma unroll
-    for (int wi = 0; wi < DC_WARPS; ++wi) {
-      const float mw = red_m[wi * 16 + row];
-      const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
-      L += red_l[wi * 16 + row] * f;
-      O += red_o[((size_t)wi * 16 + row) * D + d] * f;
-    }
-    if (single) {
-      a.out[((size_t)seq * a.nq + h0 + row) * D + d] = __float2bfloat16(O / L);
-    } else {
-      const size_t p = ((size_t)seq * a.nq + h0 + row) * a.n_splits + split;
-      a.part_o[p * D + d] = O;
-      if (d == 0) {
-        a.part_ml[p * 2] = M;
-        a.part_ml[p * 2 + 1] = L;
+    for (int sp = 0; sp < a.n_splits; ++sp) {
+      const float m = __ldcg(a.part_ml + (p0 + sp) * 2);
+      if (m != -INFINITY) {
+        const float f = exp2f(m - M);
+        L += __ldcg(a.part_ml + (p0 + sp) * 2 + 1) * f;
+        O += __ldcg(a.part_o + (p0 + sp) * D + d) * f;
       }
     }
+    a.out[((size_t)seq * a.nq + h0 + row) * D + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
   }
-}
-
-// out[seq, h, :] from the splits' partials; one block per (sequence, head).
-__global__ void attn_decode_merge_kernel(const float* __restrict__ part_o,
-                                         const float* __restrict__ part_ml, bf16* __restrict__ out,
-                                         int n_splits, int D) {
-  const size_t p0 = (size_t)blockIdx.x * n_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
-  float L = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float m = part_ml[(p0 + s) * 2];
-    if (m != -INFINITY) L += part_ml[(p0 + s) * 2 + 1] * exp2f(m - M);
-  }
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float O = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float m = part_ml[(p0 + s) * 2];
-      if (m != -INFINITY) O += part_o[(p0 + s) * D + d] * exp2f(m - M);
-    }
-    out[(size_t)blockIdx.x * D + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
-  }
+  if (tid == 0) a.counters[seq * a.nkv + kvh] = 0u;   // ready for the next launch
 }
 
 template <int DT>
@@ -207,12 +221,8 @@ static int launch(const DecodeArgs& a, cudaStream_t s) {
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  attn_decode_kernel<DT><<<dim3(a.n_splits, a.nkv, a.n_seqs), DC_THREADS, smem, s>>>(a);
-  int e = gb_status();
-  if (e || a.n_splits == 1) return e;
-  attn_decode_merge_kernel<<<a.n_seqs * a.nq, D < 128 ? D : 128, 0, s>>>(a.part_o, a.part_ml, a.out,
-                                                                         a.n_splits, D);
-  return gb_status();
+  return gb_launch(attn_decode_kernel<DT>, dim3(a.n_splits, a.nkv, a.n_seqs), dim3(DC_THREADS), smem,
+                   s, a);
 }
 
 // Refuses (GB_ERR_UNSUPPORTED) head sizes that are no multiple of 16 or above
@@ -222,7 +232,7 @@ GB_EXPORT int gb_attn_decode_bf16(const DecodeArgs* a, int D, cudaStream_t s) {
   if (a->n_seqs < 0 || a->nq <= 0 || a->nkv <= 0 || a->nq % a->nkv || a->max_pages <= 0 ||
       a->n_splits <= 0)
     return GB_ERR_BAD_ARG;
-  if (a->n_splits > 1 && (!a->part_o || !a->part_ml)) return GB_ERR_BAD_ARG;
+  if (a->n_splits > 1 && (!a->part_o || !a->part_ml || !a->counters)) return GB_ERR_BAD_ARG;
   if (D % 16 || D < 16 || D > 128 || a->nq / a->nkv > 16 || a->page % DC_BN) return GB_ERR_UNSUPPORTED;
   if (a->n_seqs > 65535 || a->nkv > 65535) return GB_ERR_UNSUPPORTED;
   if (a->n_seqs == 0) return 0;

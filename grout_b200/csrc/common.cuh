@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define GB_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -62,6 +63,46 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int gb_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch ------------------------------------------
+// A decode step is a chain of short kernels.  Launched with the "programmatic
+// stream serialization" attribute, a kernel may become resident while the one
+// before it is still draining, do whatever does not depend on that kernel (set
+// up addresses, start streaming weights, which no kernel writes), and only then
+// wait for it.  pdl_wait() returns once every kernel launched before this one
+// has finished and its writes are visible; every kernel that uses it calls it
+// before its first read of another kernel's output and before its first global
+// write.  pdl_launch_dependents() lets the next kernel in the stream start
+// early; it is called on entry.  Without the launch attribute both are no-ops.
+// The attribute is left off when GROUT_B200_NO_PDL is set in the environment.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+static inline bool gb_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) on = getenv("GROUT_B200_NO_PDL") ? 0 : 1;
+  return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int gb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = gb_pdl_enabled() ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaGetLastError();
+}
 
 // Address of row `pos` of kv head `h` of a sequence in a paged cache laid out
 // [n_pages, n_kv_heads, page, D]; `table` is the sequence's row of the block table.

@@ -8,7 +8,9 @@
 // out[r, i] = g / (1 + exp(-g)) * u in 32-bit, one rounding at the store
 // (the reference's silu_mul_2d_f16, src/kernels.rs:271-296).
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int I, int group) {
+__global__ void silu_mul_kernel(const T* in, T* __restrict__ out, int I, int group) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t r = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= I) return;
@@ -32,8 +34,8 @@ static int silu_mul(const void* in, void* out, int n_rows, int I, int group, cud
     }
     return 0;
   }
-  silu_mul_kernel<T><<<dim3((I + 255) / 256, n_rows), 256, 0, s>>>((const T*)in, (T*)out, I, group);
-  return gb_status();
+  return gb_launch(silu_mul_kernel<T>, dim3((I + 255) / 256, n_rows), dim3(256), 0, s,
+                   (const T*)in, (T*)out, I, group);
 }
 GB_EXPORT int gb_silu_mul_f32(const void* in, void* out, int n_rows, int I, int group,
                               cudaStream_t s) {

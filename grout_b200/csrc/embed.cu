@@ -3,8 +3,10 @@
 #include "common.cuh"
 
 template <typename T>
-__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+__global__ void embed_kernel(const T* __restrict__ table, const int* ids,
                              T* __restrict__ out, int H, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < V;  // an id outside the table gives a zero row
@@ -26,8 +28,8 @@ static int embed_launch(const void* table, const int* ids, void* out, int n_toke
                         cudaStream_t stream) {
   if (n_tokens < 0 || H <= 0 || V <= 0) return GB_ERR_BAD_ARG;
   if (n_tokens == 0) return 0;
-  embed_kernel<T><<<n_tokens, 256, 0, stream>>>((const T*)table, ids, (T*)out, H, V);
-  return gb_status();
+  return gb_launch(embed_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)table, ids,
+                   (T*)out, H, V);
 }
 
 GB_EXPORT int gb_embed_f32(const void* table, const int* ids, void* out, int n_tokens, int H, int V,

@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_kernel(const SkinnyArgs a) 
   constexpr int ROWS = 16 * MT, COLS = 8 * NT;
   __shared__ float red[COLS][ROWS + 1];
   __shared__ int is_last;
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int tile = blockIdx.x, split = blockIdx.y;
   const int r0 = tile * ROWS;
@@ -97,8 +98,11 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_kernel(const SkinnyArgs a) 
   const int c_begin = split * a.chunks_per_split;
   const int c_end = min(nchunks, c_begin + a.chunks_per_split);
   // UNROLL chunks are fetched before any of them is multiplied, so that a warp
-  // keeps UNROLL * (2 MT + NT) 16-byte loads in flight
-  for (int c = c_begin + warp; c < c_end; c += SK_WARPS * UNROLL) {
+  // keeps UNROLL * (2 MT + NT) 16-byte loads in flight.  The first batch of
+  // weights is requested before the kernel waits for its producer: weights are
+  // no kernel's output, the activations are.
+  bool waited = false;
+  for (int c = c_begin + warp; c < c_end || !waited; c += SK_WARPS * UNROLL) {
     uint4 wv[UNROLL][MT][2], xv[UNROLL][NT];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
@@ -110,10 +114,20 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_kernel(const SkinnyArgs a) 
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf)
           wv[u][i][hf] = (kok && wok[i][hf]) ? ld_stream(wrow[i][hf] + k) : make_uint4(0, 0, 0, 0);
+    }
+    if (!waited) {
+      pdl_wait();
+      waited = true;
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int cu = c + u * SK_WARPS;
+      const int k = cu * 32 + t * 8;
+      const bool kok = cu < c_end && k < K;
 #pragma unroll
       for (int j = 0; j < NT; ++j)
-        xv[u][j] = (kok && xok[j]) ? __ldg(reinterpret_cast<const uint4*>(xrow[j] + k))
-                                   : make_uint4(0, 0, 0, 0);
+        xv[u][j] = (kok && xok[j]) ? __ldcg(reinterpret_cast<const uint4*>(xrow[j] + k))
+                                   : make_uint4(0, 0, 0, 0);   // written by the producer: read at L2
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
@@ -193,8 +207,7 @@ template <int NT, int MT, int UNROLL, typename OutT, bool SILU>
 static int launch(const SkinnyArgs& a, cudaStream_t s) {
   const int rows = 16 * MT;
   dim3 grid((a.N + rows - 1) / rows, a.ksplit);
-  skinny_kernel<NT, MT, UNROLL, OutT, SILU><<<grid, SK_THREADS, 0, s>>>(a);
-  return gb_status();
+  return gb_launch(skinny_kernel<NT, MT, UNROLL, OutT, SILU>, grid, dim3(SK_THREADS), 0, s, a);
 }
 
 template <typename OutT, bool SILU>

@@ -13,10 +13,12 @@
 #include "common.cuh"
 
 template <typename T, typename WT>
-__global__ void add_rmsnorm_kernel(const float* res_in, const T* __restrict__ delta,
+__global__ void add_rmsnorm_kernel(const float* res_in, const T* delta,
                                    const int* __restrict__ rows, const WT* __restrict__ w,
                                    float eps, float* res_out, T* __restrict__ y, int N) {
   __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const size_t s = rows ? (size_t)rows[r] : (size_t)r;
   const float* rin = res_in ? res_in + s * N : nullptr;
@@ -69,10 +71,19 @@ template <> struct Vec4<bf16> {
 };
 
 template <typename T, typename WT>
-__global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* __restrict__ delta,
+__global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta,
                                        const int* __restrict__ rows, const WT* __restrict__ w,
                                        float eps, float* res_out, T* __restrict__ y, int N) {
   __shared__ float scratch[32];
+  pdl_launch_dependents();
+  // the weight vector is no kernel's output: fetch it while the producer drains
+  float wv[NV_MAX][4];
+#pragma unroll
+  for (int j = 0; j < NV_MAX; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+    if (i < N) Vec4<WT>::load(w + i, wv[j]);
+  }
+  pdl_wait();
   const int r = blockIdx.x;
   const size_t s = rows ? (size_t)rows[r] : (size_t)r;
   const float* rin = res_in ? res_in + s * N : nullptr;
@@ -102,10 +113,9 @@ __global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* __restrict_
   for (int j = 0; j < NV_MAX; ++j) {
     const int i = (threadIdx.x + j * blockDim.x) * 4;
     if (i < N) {
-      float wv[4], o[4];
-      Vec4<WT>::load(w + i, wv);
+      float o[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) o[e] = v[j][e] * inv * wv[e];
+      for (int e = 0; e < 4; ++e) o[e] = v[j][e] * inv * wv[j][e];
       Vec4<T>::store(yo + i, o);
     }
   }
@@ -133,13 +143,11 @@ static int launch(const float* res_in, const void* delta, const int* rows, const
     threads = ((threads + 31) / 32) * 32;
     if (threads < 64) threads = 64;
     if (threads > 1024) threads = 1024;
-    add_rmsnorm_vec_kernel<T, WT><<<n_rows, threads, 0, stream>>>(
-        res_in, (const T*)delta, rows, (const WT*)w, eps, res_out, (T*)y, N);
-    return gb_status();
+    return gb_launch(add_rmsnorm_vec_kernel<T, WT>, dim3(n_rows), dim3(threads), 0, stream, res_in,
+                     (const T*)delta, rows, (const WT*)w, eps, res_out, (T*)y, N);
   }
-  add_rmsnorm_kernel<T, WT><<<n_rows, norm_threads(N), 0, stream>>>(
-      res_in, (const T*)delta, rows, (const WT*)w, eps, res_out, (T*)y, N);
-  return gb_status();
+  return gb_launch(add_rmsnorm_kernel<T, WT>, dim3(n_rows), dim3(norm_threads(N)), 0, stream, res_in,
+                   (const T*)delta, rows, (const WT*)w, eps, res_out, (T*)y, N);
 }
 
 // w_is_f32: the weight vector is stored in 32-bit although the activations are bf16.

@@ -28,6 +28,8 @@ struct QkPrepareArgs {
 template <typename T, typename WT>
 __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
   extern __shared__ float sm[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int n_heads = a.nq + 2 * a.nkv;
@@ -88,8 +90,7 @@ static int launch(const QkPrepareArgs& a, cudaStream_t stream) {
   dim3 grid(a.n_tokens, (n_heads + warps - 1) / warps);
   const size_t smem = (size_t)warps * a.D * sizeof(float);
   if (smem > 48 * 1024) return GB_ERR_UNSUPPORTED;
-  qk_prepare_kernel<T, WT><<<grid, warps * 32, smem, stream>>>(a);
-  return gb_status();
+  return gb_launch(qk_prepare_kernel<T, WT>, grid, dim3(warps * 32), smem, stream, a);
 }
 
 static int check(const QkPrepareArgs& a) {

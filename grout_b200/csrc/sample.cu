@@ -60,9 +60,11 @@ __device__ ArgBest block_argmax(const float* row, int V, float mul, ArgBest* sh)
   return r;
 }
 
-__global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ logits, int V,
+__global__ void __launch_bounds__(ST) argmax_kernel(const float* logits, int V,
                                                     int* __restrict__ out) {
   __shared__ ArgBest sh[ST / 32];
+  pdl_launch_dependents();
+  pdl_wait();
   const ArgBest r = block_argmax(logits + (size_t)blockIdx.x * V, V, 1.0f, sh);
   if (threadIdx.x == 0) out[blockIdx.x] = r.i;
 }
@@ -70,8 +72,7 @@ __global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ lo
 GB_EXPORT int gb_argmax_f32(const float* logits, int n_rows, int V, int* out, cudaStream_t s) {
   if (n_rows < 0 || V <= 0) return GB_ERR_BAD_ARG;
   if (n_rows == 0) return 0;
-  argmax_kernel<<<n_rows, ST, 0, s>>>(logits, V, out);
-  return gb_status();
+  return gb_launch(argmax_kernel, dim3(n_rows), dim3(ST), 0, s, logits, V, out);
 }
 
 // ---------------------------------------------------------------------------

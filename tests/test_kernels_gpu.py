@@ -274,7 +274,8 @@ def test_gemm_skinny_silu_epilogue(M, I, K):
     # the stand-alone kernel on the same interleaved layout agrees
     raw = _ops().gemm_skinny_bf16(x.to(DEV), w.to(DEV), torch.float32)
     two = _ops().silu_mul(raw, 8).cpu()
-    assert torch.allclose(two.double(), want, atol=1e-5, rtol=1e-5)
+    # 32-bit sums over K, then the product of two such values
+    assert torch.allclose(two.double(), want, atol=8e-5 * math.sqrt(K), rtol=1e-5)
 
 
 def test_gemm_skinny_row_independent():
