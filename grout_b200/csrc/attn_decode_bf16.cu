@@ -8,10 +8,8 @@
 // block-wide barrier sits in the key loop.  The warps' (max, sum, accumulator)
 // are merged in shared memory.  With one split the block writes the output;
 // otherwise it writes a 32-bit partial (accumulator relative to its max, max,
-// sum) to scratch and bumps the counter of its (sequence, kv head); the block
-// that arrives last combines the splits in split order:
-//   out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),  M = max_s m_s,
-// and leaves the counter at zero.  No block waits for another.
+// sum) to scratch and a second, wide kernel combines the splits in split order:
+//   out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M),  M = max_s m_s.
 // The key range of a sequence comes from kv_len on the device, so one captured
 // launch serves every step.  (The reference's pair is fmha_decode_gqa_split +
 // splitk_reduce_merge, src/kernels.rs:2586-2749, 2771-2868, which stores f16
@@ -32,7 +30,6 @@ struct DecodeArgs {
   bf16* out;               // [n_seqs, nq, D]
   float* part_o;           // [n_seqs, nq, n_splits, D]   (n_splits > 1)
   float* part_ml;          // [n_seqs, nq, n_splits, 2]
-  unsigned* counters;      // [n_seqs, nkv], zero before the first launch   (n_splits > 1)
   int n_seqs, nq, nkv, max_pages, page, window, n_splits;
   float scale_log2;
 };
@@ -41,10 +38,8 @@ template <int DT>
 __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArgs a) {
   constexpr int D = 16 * DT, LD = D + 8, CHUNKS = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ int is_last;
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);       // [16][LD]
   bf16* kv_s = q_s + 16 * LD;                          // per warp: [2 stages][K, V][32][LD]
-  pdl_launch_dependents();
   pdl_wait();   // queries and the newest keys are the producer's output
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
@@ -130,6 +125,7 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
       __syncwarp();  // all lanes are done with the stage before it is refilled
     }
     cp_async_wait<0>();
+    pdl_launch_dependents();   // the key stream of this block is over
     w.finish_l();
     __syncthreads();  // every warp has left its buffers: reuse them for the merge
 
@@ -177,35 +173,31 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
       }
     }
   }
-  if (single) return;
+}
 
-  // the block that arrives last combines the splits of its (sequence, kv head)
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const unsigned old = atomicAdd(&a.counters[seq * a.nkv + kvh], 1u);
-    is_last = (old == (unsigned)a.n_splits - 1u);
+// out[seq, h, :] from the splits' partials; one block per (sequence, head).
+// A separate, wide launch: the combination is a few hundred independent loads
+// per output row, which one block per kv head would have to do alone.
+__global__ void attn_decode_merge_kernel(const float* part_o, const float* part_ml,
+                                         bf16* __restrict__ out, int n_splits, int D) {
+  pdl_wait();
+  const size_t p0 = (size_t)blockIdx.x * n_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float m = part_ml[(p0 + s) * 2];
+    if (m != -INFINITY) L += part_ml[(p0 + s) * 2 + 1] * exp2f(m - M);
   }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  for (int i = tid; i < G * D; i += DC_THREADS) {
-    const int row = i / D, d = i % D;
-    const size_t p0 = ((size_t)seq * a.nq + h0 + row) * a.n_splits;
-    float M = -INFINITY;
-    for (int sp = 0; sp < a.n_splits; ++sp) M = fmaxf(M, __ldcg(a.part_ml + (p0 + sp) * 2));
-    float L = 0.f, O = 0.f;
-    for (int sp = 0; sp < a.n_splits; ++sp) {
-      const float m = __ldcg(a.part_ml + (p0 + sp) * 2);
-      if (m != -INFINITY) {
-        const float f = exp2f(m - M);
-        L += __ldcg(a.part_ml + (p0 + sp) * 2 + 1) * f;
-        O += __ldcg(a.part_o + (p0 + sp) * D + d) * f;
-      }
+  pdl_launch_dependents();
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float O = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float m = part_ml[(p0 + s) * 2];
+      if (m != -INFINITY) O += part_o[(p0 + s) * D + d] * exp2f(m - M);
     }
-    a.out[((size_t)seq * a.nq + h0 + row) * D + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+    out[(size_t)blockIdx.x * D + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
   }
-  if (tid == 0) a.counters[seq * a.nkv + kvh] = 0u;   // ready for the next launch
 }
 
 template <int DT>
@@ -221,8 +213,11 @@ static int launch(const DecodeArgs& a, cudaStream_t s) {
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return gb_launch(attn_decode_kernel<DT>, dim3(a.n_splits, a.nkv, a.n_seqs), dim3(DC_THREADS), smem,
-                   s, a);
+  int e = gb_launch(attn_decode_kernel<DT>, dim3(a.n_splits, a.nkv, a.n_seqs), dim3(DC_THREADS),
+                    smem, s, a);
+  if (e || a.n_splits == 1) return e;
+  return gb_launch(attn_decode_merge_kernel, dim3(a.n_seqs * a.nq), dim3(D < 128 ? D : 128), 0, s,
+                   (const float*)a.part_o, (const float*)a.part_ml, a.out, a.n_splits, D);
 }
 
 // Refuses (GB_ERR_UNSUPPORTED) head sizes that are no multiple of 16 or above
@@ -232,7 +227,7 @@ GB_EXPORT int gb_attn_decode_bf16(const DecodeArgs* a, int D, cudaStream_t s) {
   if (a->n_seqs < 0 || a->nq <= 0 || a->nkv <= 0 || a->nq % a->nkv || a->max_pages <= 0 ||
       a->n_splits <= 0)
     return GB_ERR_BAD_ARG;
-  if (a->n_splits > 1 && (!a->part_o || !a->part_ml || !a->counters)) return GB_ERR_BAD_ARG;
+  if (a->n_splits > 1 && (!a->part_o || !a->part_ml)) return GB_ERR_BAD_ARG;
   if (D % 16 || D < 16 || D > 128 || a->nq / a->nkv > 16 || a->page % DC_BN) return GB_ERR_UNSUPPORTED;
   if (a->n_seqs > 65535 || a->nkv > 65535) return GB_ERR_UNSUPPORTED;
   if (a->n_seqs == 0) return 0;

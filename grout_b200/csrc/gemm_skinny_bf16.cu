@@ -61,7 +61,6 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_kernel(const SkinnyArgs a) 
   constexpr int ROWS = 16 * MT, COLS = 8 * NT;
   __shared__ float red[COLS][ROWS + 1];
   __shared__ int is_last;
-  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int tile = blockIdx.x, split = blockIdx.y;
   const int r0 = tile * ROWS;
@@ -141,6 +140,8 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_kernel(const SkinnyArgs a) 
                    xv[u][j].z, xv[u][j].w);
         }
   }
+
+  pdl_launch_dependents();   // the weight stream of this block is over
 
   // sum the warps' partial tiles in warp order
   for (int w = 0; w < SK_WARPS; ++w) {

@@ -28,6 +28,7 @@ from typing import Dict, Iterable, List
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
+NVCC_FLAGS += os.environ.get("GROUT_B200_NVCC_FLAGS", "").split()   # e.g. -DNAME for experiments
 
 _LOCK = threading.Lock()
 _LOADED: Dict[str, ctypes.CDLL] = {}

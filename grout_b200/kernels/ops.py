@@ -43,7 +43,8 @@ _LAUNCHES = 0
 
 
 def launch_count() -> int:
-    """Kernel launches made through this module so far."""
+    """Kernel launches made through this module so far (a decode-attention call
+    with more than one split counts its merge kernel too)."""
     return _LAUNCHES
 
 
@@ -388,8 +389,7 @@ class _PrefillArgs(ctypes.Structure):
 
 class _DecodeArgs(ctypes.Structure):
     _fields_ = [("q", _P), ("k_pages", _P), ("v_pages", _P), ("block_table", _P), ("slots", _P),
-                ("kv_len", _P), ("out", _P), ("part_o", _P), ("part_ml", _P), ("counters", _P),
-                ("n_seqs", _I),
+                ("kv_len", _P), ("out", _P), ("part_o", _P), ("part_ml", _P), ("n_seqs", _I),
                 ("nq", _I), ("nkv", _I), ("max_pages", _I), ("page", _I), ("window", _I),
                 ("n_splits", _I), ("scale_log2", _F)]
 
@@ -466,22 +466,21 @@ def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: i
         raise KernelError("one slot and one length per query row are needed")
     ns = int(n_splits) if n_splits else decode_splits(B, nkv, max_kv_len, q.device)
     out = torch.empty_like(q)
-    part_o = part_ml = counters = None
+    part_o = part_ml = None
     if ns > 1:
-        # scratch of the split: partials of every (sequence, head, split), and one
-        # arrival counter per (sequence, kv head) that the kernel leaves at zero
+        # scratch of the split: 32-bit partials of every (sequence, head, split)
         ws = _WORKSPACES.setdefault(q.device.index or 0, _Workspace())
-        scratch, counters = ws.get(q.device, B * nq * ns * (D + 2), B * nkv)
+        scratch, _counters = ws.get(q.device, B * nq * ns * (D + 2), 1)
         part_o = scratch[:B * nq * ns * D]
         part_ml = scratch[B * nq * ns * D:B * nq * ns * (D + 2)]
     a = _DecodeArgs()
     a.q, a.k_pages, a.v_pages, a.block_table = q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr()
     a.slots, a.kv_len, a.out = slots.data_ptr(), kv_len.data_ptr(), out.data_ptr()
-    a.part_o, a.part_ml, a.counters = _ptr(part_o), _ptr(part_ml), _ptr(counters)
+    a.part_o, a.part_ml = _ptr(part_o), _ptr(part_ml)
     a.n_seqs, a.nq, a.nkv, a.max_pages, a.page = B, nq, nkv, block_table.shape[1], page
     a.window, a.n_splits, a.scale_log2 = int(window or 0), ns, float(scale) * _LOG2E
     _check(_fn("attn_decode_bf16", "gb_attn_decode_bf16", "pip")(
-        ctypes.addressof(a), D, _stream()), "attn_decode_bf16")
+        ctypes.addressof(a), D, _stream()), "attn_decode_bf16", 2 if ns > 1 else 1)
     return out
 
 
