@@ -239,3 +239,93 @@ GB_EXPORT int gb_gemm_skinny_bf16(const SkinnyArgs* a, int out_f32, int silu, cu
   if (silu) return out_f32 ? dispatch<float, true>(*a, s) : dispatch<bf16, true>(*a, s);
   return out_f32 ? dispatch<float, false>(*a, s) : dispatch<bf16, false>(*a, s);
 }
+
+// ---------------------------------------------------------------------------
+// The same product for callers that cannot allocate: see gemm_skinny_noalloc.h.
+// The scratch is the two static device arrays below; in host code their names
+// stand for the symbols, not for device addresses, so the addresses are looked
+// up once per device and passed to the kernel like any other pointer.
+#include <mutex>
+#include "gemm_skinny_noalloc.h"
+
+static __device__ __align__(256) float gb_noalloc_scratch[GB_NOALLOC_SCRATCH_FLOATS];
+static __device__ __align__(256) unsigned gb_noalloc_counters[GB_NOALLOC_MAX_TILES];
+
+struct NoAllocDevice {
+  float* scratch = nullptr;
+  unsigned* counters = nullptr;
+  int sm_count = 0;
+  bool ready = false;
+};
+static NoAllocDevice g_noalloc[GB_NOALLOC_MAX_DEVICES];
+static std::mutex g_noalloc_mutex;
+
+// Once per device, with that device current.
+static int noalloc_setup(int dev, NoAllocDevice** out) {
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  NoAllocDevice& d = g_noalloc[dev];
+  if (!d.ready) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, gb_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    d.scratch = (float*)p;
+    e = cudaGetSymbolAddress(&p, gb_noalloc_counters);
+    if (e != cudaSuccess) return (int)e;
+    d.counters = (unsigned*)p;
+    e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    d.ready = true;
+  }
+  *out = &d;
+  return 0;
+}
+
+GB_EXPORT int gb_gemm_skinny_bf16_noalloc(const void* x, const void* W, void* y, int M, int N,
+                                          int K, int out_f32, cudaStream_t stream) {
+  if (M < 0 || N <= 0 || K <= 0 || !x || !W || !y) return GB_ERR_BAD_ARG;
+  if (M > 64 || (K % 8)) return GB_ERR_UNSUPPORTED;
+  if ((((uintptr_t)x) | ((uintptr_t)W)) & 15) return GB_ERR_BAD_ARG;
+  if (M == 0) return 0;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= GB_NOALLOC_MAX_DEVICES) return GB_ERR_UNSUPPORTED;
+  NoAllocDevice* d = nullptr;
+  int rc = noalloc_setup(dev, &d);
+  if (rc) return rc;
+
+  // the split the allocating path uses: about eight blocks per SM, at least 16
+  // chunks of 32 elements per block, at most 16 splits
+  const int rows = gb_gemm_skinny_tile_rows(M), cols = gb_gemm_skinny_tile_cols(M);
+  const int tiles = (N + rows - 1) / rows;
+  const int nchunks = (K + 31) / 32;
+  int ks = (8 * d->sm_count + tiles - 1) / tiles;
+  if (ks > nchunks / 16) ks = nchunks / 16;
+  if (ks > 16) ks = 16;
+  if (ks < 1) ks = 1;
+  const int per = (nchunks + ks - 1) / ks;
+  ks = (nchunks + per - 1) / per;
+
+  SkinnyArgs a;
+  a.x = (const bf16*)x;
+  a.W = (const bf16*)W;
+  a.y = y;
+  a.scratch = nullptr;
+  a.counters = nullptr;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ksplit = ks;
+  a.chunks_per_split = per;
+  if (ks > 1) {
+    if (tiles > GB_NOALLOC_MAX_TILES ||
+        (long long)tiles * ks * rows * cols > (long long)GB_NOALLOC_SCRATCH_FLOATS)
+      return GB_ERR_TOO_LARGE;
+    a.scratch = d->scratch;
+    a.counters = d->counters;
+    // the array keeps the last call's contents: the counters must start at zero
+    e = cudaMemsetAsync(d->counters, 0, (size_t)tiles * sizeof(unsigned), stream);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return out_f32 ? dispatch<float, false>(a, stream) : dispatch<bf16, false>(a, stream);
+}
