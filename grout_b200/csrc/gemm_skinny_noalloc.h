@@ -12,8 +12,8 @@
 // What it computes is exactly what gb_gemm_skinny_bf16 computes without the
 // SiLU epilogue:  y[M, N] = x[M, K] . W[N, K]^T,  bf16 inputs, 32-bit sums,
 // M <= 64, K a multiple of 8, x and W 16-byte aligned.  The caller passes the
-// inputs and the output; the split-K scratch (32-bit partial tiles and one
-// arrival counter per tile of weight rows) lives in two file-scope
+// inputs and the output; the scratch of the work split (two 32-bit partial
+// tiles per block and one arrival counter per tile of weight rows) lives in two file-scope
 // `static __device__` arrays inside the library instead of in buffers from an
 // allocator:
 //
@@ -21,9 +21,10 @@
 //   (64 KiB).  Every GPU on which the library is loaded holds them until the
 //   process exits, whether or not this function is ever called.
 //
-// A shape whose partial tiles or tile count exceed those sizes is refused with
+// A launch whose partial tiles or tile count exceed those sizes is refused with
 // GB_ERR_TOO_LARGE (-3) and nothing is launched; use the allocating entry point
-// for it.  (With 148 SMs: N = 2560, K = 9728 fits for M <= 16; M = 32 and 64 do not.)
+// for it.  (On a GPU with 148 SMs every shape with M <= 16 and up to 16384 tiles
+// of weight rows fits; M > 16 does not: its tiles are 32 rows by 32 or 64.)
 //
 // The call itself makes no cudaMalloc, cudaFree or other allocating call.  The
 // first call on each device looks up the arrays' device addresses

@@ -300,14 +300,14 @@ SKINNY_MAX_ROWS = 64
 
 class _SkinnyArgs(ctypes.Structure):
     _fields_ = [("x", _P), ("W", _P), ("y", _P), ("scratch", _P), ("counters", _P), ("M", _I),
-                ("N", _I), ("K", _I), ("ksplit", _I), ("chunks_per_split", _I)]
+                ("N", _I), ("K", _I)]
 
 
 class _Workspace:
-    """Scratch of the split-K product, one per device: 32-bit partial tiles and
-    one arrival counter per tile.  The counters are zero between launches (the
-    kernel leaves them so).  Launches that share it must be ordered on one
-    stream, which every step of this library is."""
+    """Scratch of the kernels that split a sum over blocks, one per device:
+    32-bit partial tiles and arrival counters.  The counters are zero between
+    launches (the kernels leave them so).  Launches that share it must be ordered
+    on one stream, which every step of this library is."""
 
     def __init__(self):
         self.scratch = None
@@ -320,25 +320,27 @@ class _Workspace:
             self.scratch = torch.empty(max(n_floats, 1 << 22), dtype=torch.float32, device=device)
         if self.counters is None or self.counters.numel() < n_counters:
             self._kept.append(self.counters)
-            self.counters = torch.zeros(max(n_counters, 1 << 14), dtype=torch.int32, device=device)
+            self.counters = torch.zeros(max(n_counters, 1 << 16), dtype=torch.int32, device=device)
         return self.scratch, self.counters
 
 
 _WORKSPACES = {}
+_SKINNY_PLANS = {}
 
 
-def skinny_split(M: int, N: int, K: int, device) -> Tuple[int, int, int]:
-    """(ksplit, chunks per split, tiles): K is cut over enough blocks that about
-    eight four-warp blocks per SM are resident, as long as every block keeps at
-    least 16 chunks of 32 elements.  It depends on N, K and M's bucket only."""
-    rows = 16 if M <= 16 else 32
-    tiles = (N + rows - 1) // rows
-    nchunks = (K + 31) // 32
-    want = (8 * _sm_count(device) + tiles - 1) // tiles
-    ks = max(1, min(want, nchunks // 16, 16))
-    per = (nchunks + ks - 1) // ks
-    ks = (nchunks + per - 1) // per
-    return ks, per, tiles
+def skinny_plan(M: int, N: int, K: int, out_f32: bool, silu: bool):
+    """(blocks, scratch floats, counters) of the decode product for this shape:
+    as many blocks as the GPU holds at once, each streaming an equal share of the
+    weights; it depends on N, K and M's bucket (<= 8, 16, 32, 64) only."""
+    bucket = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
+    key = (bucket, N, K, bool(out_f32), bool(silu), torch.cuda.current_device())
+    plan = _SKINNY_PLANS.get(key)
+    if plan is None:
+        out = (c_int * 3)()
+        _check(_fn("gemm_skinny_bf16", "gb_gemm_skinny_plan", "iiiiip")(
+            bucket, N, K, int(out_f32), int(silu), ctypes.addressof(out)), "gemm_skinny_plan", 0)
+        plan = _SKINNY_PLANS[key] = (out[0], out[1], out[2])
+    return plan
 
 
 def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
@@ -363,19 +365,17 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
     y = torch.empty((M, N // 2 if silu_mul else N), dtype=out_dtype, device=x.device)
     if M == 0:
         return y
-    ks, per, tiles = skinny_split(M, N, K, x.device)
-    a = _SkinnyArgs()
-    a.x, a.W, a.y = x.data_ptr(), w.data_ptr(), y.data_ptr()
-    a.M, a.N, a.K, a.ksplit, a.chunks_per_split = M, N, K, ks, per
-    if ks > 1:
-        rows = 16 if M <= 16 else 32
-        cols = 8 if M <= 8 else 16 if M <= 16 else 32 if M <= 32 else 64
+    with torch.cuda.device(x.device):
+        _blocks, n_floats, n_counters = skinny_plan(M, N, K, out_dtype == torch.float32, silu_mul)
         ws = _WORKSPACES.setdefault(x.device.index or 0, _Workspace())
-        scratch, counters = ws.get(x.device, tiles * ks * rows * cols, tiles)
+        scratch, counters = ws.get(x.device, n_floats, n_counters)
+        a = _SkinnyArgs()
+        a.x, a.W, a.y = x.data_ptr(), w.data_ptr(), y.data_ptr()
         a.scratch, a.counters = scratch.data_ptr(), counters.data_ptr()
-    _check(_fn("gemm_skinny_bf16", "gb_gemm_skinny_bf16", "piip")(
-        ctypes.addressof(a), int(out_dtype == torch.float32), int(silu_mul), _stream()),
-        "gemm_skinny_bf16")
+        a.M, a.N, a.K = M, N, K
+        _check(_fn("gemm_skinny_bf16", "gb_gemm_skinny_bf16", "piip")(
+            ctypes.addressof(a), int(out_dtype == torch.float32), int(silu_mul), _stream()),
+            "gemm_skinny_bf16")
     return y
 
 

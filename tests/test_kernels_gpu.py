@@ -246,10 +246,13 @@ def test_gemm_skinny_bf16(M, N, K, out):
 
 @pytest.mark.parametrize("M,N,K", [(8, 2560, 9728), (3, 160, 4096), (40, 2560, 4096), (16, 6144, 2560)])
 def test_gemm_skinny_split_k(M, N, K):
-    """Shapes whose K is split over several blocks (partials in scratch, the last
-    block sums them); called twice, since the arrival counters must be left at zero."""
+    """Shapes whose tiles are shared by several blocks (partials in scratch, the
+    block that arrives last sums them); called twice, since the arrival counters
+    must be left at zero."""
     ops = _ops()
-    assert ops.skinny_split(M, N, K, DEV)[0] > 1
+    blocks, n_floats, n_counters = ops.skinny_plan(M, N, K, True, False)
+    rows = 16 if M <= 16 else 32
+    assert blocks > (N + rows - 1) // rows and n_floats > 0
     x, w = _rand((M, K), torch.bfloat16, 32), _rand((N, K), torch.bfloat16, 33, 0.05)
     want = x.double() @ w.double().T
     first = ops.gemm_skinny_bf16(x.to(DEV), w.to(DEV), torch.float32).cpu()
