@@ -1,0 +1,573 @@
+// bf16 matrix product on the fifth-generation tensor cores:
+//   C[rowsA, rowsB] = A[rowsA, K] . B[rowsB, K]^T,  32-bit accumulate,
+// with both operands K-major (row-major [rows, K]), which is how activations
+// [tokens, in] and weights [out, in] are stored.  The same kernel serves
+//   prefill:  A = activations, B = weights, out[token, feature]          and
+//   decode:   A = weights, B = the few activation rows, out transposed,
+// so that the long dimension always fills the 128 rows of the MMA ("swap A/B").
+// The reference calls cuBLAS GemmEx for these products (src/cublas.rs:287-307).
+//
+// Structure (one persistent block of 192 threads per SM):
+//   warp 0    one lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte
+//             swizzle) of a 128 x 64 tile of A and a BN x 64 tile of B per stage
+//             into a ring of STAGES shared-memory stages, signalled by mbarriers;
+//   warp 1    allocates tensor memory; one lane issues tcgen05.mma
+//             (cta_group::1, kind::f16, M = 128, N = BN, K = 16, four per stage)
+//             with the accumulator in TMEM, and tcgen05.commit to free the stage;
+//   warps 2-5 read the accumulator back with tcgen05.ld (each warp its 32 lanes),
+//             convert and store.  Two accumulators alternate, so the epilogue of
+//             one tile overlaps the main loop of the next.
+// No TMA load uses cluster multicast.
+//
+// Work split ("stream-K"): tiles x k-blocks form one line of U units; block p
+// takes [p U / P, (p + 1) U / P).  A tile covered by one block is written
+// directly; a tile shared by several is finished by the block that arrives last
+// at the tile's counter, which adds the 32-bit partials (kept in scratch, two
+// slots per block) in block order.  No block waits for another block.
+//
+// Every wait on an mbarrier is bounded by a wall-clock limit; when it expires
+// the block records a code in args.error, stops issuing work, waits (bounded)
+// for its copies in flight, frees its tensor memory and returns.
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_WAIT_LIMIT_NS 2000000000ull   // 2 s: far beyond any legitimate wait
+
+#define GB_ERR_TIMEOUT_FULL 101    // MMA warp: a stage never arrived
+#define GB_ERR_TIMEOUT_EMPTY 102   // producer: a stage was never released
+#define GB_ERR_TIMEOUT_TMEM_FULL 103
+#define GB_ERR_TIMEOUT_TMEM_EMPTY 104
+
+struct TcArgs {
+  void* out;            // [rowsA, ld] or, transposed, [rowsB, ld]
+  float* scratch;       // [2 * blocks][BN][128] partial tiles
+  unsigned* counters;   // [tiles], zero before the first launch
+  int* error;           // device int, 0 while all is well
+  int rowsA, rowsB, K, ld;
+  int transpose_out, out_f32, silu;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(void* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(void* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P1;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P1;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for the phase with the given parity; false when the time limit expired
+// or (where a flag is given) another role of the block has already given up.
+__device__ __forceinline__ bool mbar_wait(void* bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns = TC_WAIT_LIMIT_NS) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = now_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try(bar, parity)) return true;
+    if (abort_flag && *abort_flag) return mbar_try(bar, parity);
+    if (now_ns() - t0 > limit_ns) return false;
+  }
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            void* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major operand tile in shared memory, rows of 64 bf16 (128 bytes) under the
+// 128-byte swizzle: groups of 8 rows are 1024 bytes apart (stride byte offset),
+// the leading byte offset is unused for swizzled K-major layouts, descriptor
+// version 1 (sm_100), layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ int tc_block_of_unit(long long u, long long U, int P) {
+  return (int)(((u + 1) * P - 1) / U);
+}
+
+template <int BN>
+struct TcConfig {
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // both multiples of 1024
+  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256;
+  // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
+  static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                    ((uint32_t)(TC_BM >> 4) << 24);
+};
+
+template <int BN>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const TcArgs a) {
+  using Cfg = TcConfig<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles_base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(tiles_base + (size_t)STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES]
+  uint64_t* empty = bars + STAGES;          // [STAGES]
+  uint64_t* acc_full = bars + 2 * STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;       // [2]
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+  __shared__ int last_s;
+  volatile int* abort_flag = &abort_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int P = gridDim.x, p = blockIdx.x;
+  const int tiles_a = (a.rowsA + TC_BM - 1) / TC_BM, tiles_b = (a.rowsB + BN - 1) / BN;
+  const int kblocks = (a.K + TC_BK - 1) / TC_BK;
+  const long long U = (long long)tiles_a * tiles_b * kblocks;
+  const long long u_begin = p * U / P, u_end = (p + 1) * U / P;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);   // one arrival per epilogue warp
+    }
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_base_s)),
+                 "r"((uint32_t)Cfg::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  pdl_wait();   // activations (and the scratch of an earlier launch) are complete
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      long long it = 0;
+      bool ok = true;
+      for (long long u = u_begin; u < u_end && ok;) {
+        const int tile = (int)(u / kblocks);
+        const int kb_lo = (int)(u - (long long)tile * kblocks);
+        const int kb_hi = (int)min((long long)kblocks, kb_lo + (u_end - u));
+        u += kb_hi - kb_lo;
+        const int ta = tile % tiles_a, tb = tile / tiles_a;
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+          const int s = (int)(it % STAGES);
+          const uint32_t round = (uint32_t)(it / STAGES);
+          if (!mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag)) {
+            if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = tiles_base + (size_t)s * Cfg::STAGE_BYTES;
+          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          tma_load_2d(sa, &map_a, kb * TC_BK, ta * TC_BM, &full[s]);
+          tma_load_2d(sa + Cfg::A_BYTES, &map_b, kb * TC_BK, tb * BN, &full[s]);
+        }
+      }
+      pdl_launch_dependents();
+      // Every load issued above completes on a `full` barrier that the MMA warp
+      // waits for (or, after an abort, that is waited for below).
+      if (!ok) {   // after an abort: let the copies in flight land before the block exits
+        for (long long j = max(0ll, it - STAGES); j < it; ++j)
+          mbar_wait(&full[j % STAGES], (uint32_t)(j / STAGES) & 1, nullptr, 100000000ull);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue
+    if (lane == 0) {
+      long long it = 0;
+      int seg = 0;
+      bool ok = true;
+      for (long long u = u_begin; u < u_end && ok; ++seg) {
+        const int tile = (int)(u / kblocks);
+        const int kb_lo = (int)(u - (long long)tile * kblocks);
+        const int kb_hi = (int)min((long long)kblocks, kb_lo + (u_end - u));
+        u += kb_hi - kb_lo;
+        const int ab = seg & 1;
+        if (!mbar_wait(&acc_empty[ab], (((uint32_t)seg >> 1) & 1) ^ 1, abort_flag)) {
+          if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_TIMEOUT_TMEM_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(ab * BN);
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
+          const int s = (int)(it % STAGES);
+          if (!mbar_wait(&full[s], (uint32_t)(it / STAGES) & 1, abort_flag)) {
+            if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_TIMEOUT_FULL);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles_base + (size_t)s * Cfg::STAGE_BYTES);
+          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + Cfg::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k)   // 16 elements = 32 bytes = 2 descriptor units
+            tc_mma(tmem_d, da + 2 * k, db + 2 * k, Cfg::IDESC, (kb > kb_lo || k > 0) ? 1u : 0u);
+          tc_commit(&empty[s]);   // the stage is free once these MMAs have read it
+        }
+        if (ok) tc_commit(&acc_full[ab]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;               // the TMEM lanes this warp may read
+    const int r = q * 32 + lane;          // row of the tile
+    const int et = threadIdx.x - 64;      // 0..127 among the epilogue threads
+    int seg = 0;
+    bool ok = true;
+    for (long long u = u_begin; u < u_end && ok; ++seg) {
+      const int tile = (int)(u / kblocks);
+      const int kb_lo = (int)(u - (long long)tile * kblocks);
+      const int kb_hi = (int)min((long long)kblocks, kb_lo + (u_end - u));
+      const long long u_seg = u;
+      u += kb_hi - kb_lo;
+      const int ta = tile % tiles_a, tb = tile / tiles_a;
+      const int ab = seg & 1;
+      // lane 0 polls for the warp, so that all lanes take the same way; the four
+      // epilogue warps wait on the same phase with the same limit and no abort
+      // flag, so they agree as well (they meet at a named barrier below)
+      int got = 0;
+      if (lane == 0) got = mbar_wait(&acc_full[ab], ((uint32_t)seg >> 1) & 1, nullptr) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (!got) {
+        if (lane == 0) {
+          atomicCAS(a.error, 0, GB_ERR_TIMEOUT_TMEM_FULL);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * BN);
+      const bool whole = kb_lo == 0 && kb_hi == kblocks;
+      const int row_a = ta * TC_BM + r;
+      bool write_out = whole;
+      int p_first = 0, p_last = 0;
+      if (!whole) {
+        // leave the partial [BN][128] in this block's slot, then see who is last
+        const bool my_first_tile = (int)(u_begin / kblocks) == tile;
+        float* mine = a.scratch + ((size_t)2 * p + (my_first_tile ? 0 : 1)) * (size_t)(BN * TC_BM);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t v[16];
+          tc_ld16(taddr + c0, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * TC_BM + r] = __uint_as_float(v[j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[ab]);   // the accumulator may be reused
+        const long long t0 = (long long)tile * kblocks;
+        p_first = tc_block_of_unit(t0, U, P);
+        p_last = tc_block_of_unit(t0 + kblocks - 1, U, P);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) {
+          const unsigned old = atomicAdd(&a.counters[tile], 1u);
+          last_s = (old == (unsigned)(p_last - p_first));
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        write_out = last_s != 0;
+        if (write_out) __threadfence();
+      }
+      (void)u_seg;
+      if (write_out) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float f[16];
+          if (whole) {
+            uint32_t v[16];
+            tc_ld16(taddr + c0, v);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(v[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) f[j] = 0.f;
+            for (int qb = p_first; qb <= p_last; ++qb) {   // block order: a fixed sum
+              const bool q_first = (int)(((long long)qb * U / P) / kblocks) == tile;
+              const float* src =
+                  a.scratch + ((size_t)2 * qb + (q_first ? 0 : 1)) * (size_t)(BN * TC_BM);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) f[j] += __ldcg(src + (size_t)(c0 + j) * TC_BM + r);
+            }
+          }
+          // store 16 columns of row r
+          if (a.transpose_out) {
+            // out[col_b][row_a]: lanes hold consecutive row_a, so each j is a coalesced store
+            if (row_a < a.rowsA) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int cb = tb * BN + c0 + j;
+                if (cb < a.rowsB) {
+                  const size_t o = (size_t)cb * a.ld + row_a;
+                  if (a.out_f32) ((float*)a.out)[o] = f[j];
+                  else ((bf16*)a.out)[o] = __float2bfloat16_rn(f[j]);
+                }
+              }
+            }
+          } else if (row_a < a.rowsA) {
+            const int cb0 = tb * BN + c0;
+            const size_t o = (size_t)row_a * a.ld + cb0;
+            if (a.out_f32) {
+              float* dst = (float*)a.out + o;
+              if (cb0 + 16 <= a.rowsB && ((uintptr_t)dst & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < 16; j += 4)
+                  *reinterpret_cast<float4*>(dst + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+              } else {
+                for (int j = 0; j < 16; ++j)
+                  if (cb0 + j < a.rowsB) dst[j] = f[j];
+              }
+            } else {
+              bf16* dst = (bf16*)a.out + o;
+              if (cb0 + 16 <= a.rowsB && ((uintptr_t)dst & 15) == 0) {
+                uint4 w0, w1;
+                w0.x = pack2(f[0], f[1]);   w0.y = pack2(f[2], f[3]);
+                w0.z = pack2(f[4], f[5]);   w0.w = pack2(f[6], f[7]);
+                w1.x = pack2(f[8], f[9]);   w1.y = pack2(f[10], f[11]);
+                w1.z = pack2(f[12], f[13]); w1.w = pack2(f[14], f[15]);
+                reinterpret_cast<uint4*>(dst)[0] = w0;
+                reinterpret_cast<uint4*>(dst)[1] = w1;
+              } else {
+                for (int j = 0; j < 16; ++j)
+                  if (cb0 + j < a.rowsB) dst[j] = __float2bfloat16_rn(f[j]);
+              }
+            }
+          }
+        }
+        if (!whole && et == 0) a.counters[tile] = 0u;   // ready for the next launch
+      }
+      if (whole) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[ab]);
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)Cfg::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- host --------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// A [rows, K] bf16 row-major operand seen as tiles of box_rows x 64 elements.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return GB_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : GB_ERR_BAD_ARG;
+}
+
+static int pick_bn(int rowsB) {
+  if (rowsB <= 16) return 16;
+  if (rowsB <= 32) return 32;
+  if (rowsB <= 64) return 64;
+  if (rowsB <= 128) return 128;
+  return 256;
+}
+
+struct TcPlan {
+  int bn, blocks, scratch_floats, counters;
+};
+
+static int tc_plan(int rowsA, int rowsB, int K, TcPlan* pl) {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int bn = pick_bn(rowsB);
+  const long long tiles = (long long)((rowsA + TC_BM - 1) / TC_BM) * ((rowsB + bn - 1) / bn);
+  const long long units = tiles * ((K + TC_BK - 1) / TC_BK);
+  if (tiles > (1 << 30)) return GB_ERR_UNSUPPORTED;
+  long long blocks = units < sms ? units : sms;
+  pl->bn = bn;
+  pl->blocks = (int)blocks;
+  pl->scratch_floats = (int)(2 * blocks * bn * TC_BM);
+  pl->counters = (int)tiles;
+  return 0;
+}
+
+template <int BN>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, int blocks,
+                  cudaStream_t s) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)TcConfig<BN>::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return gb_launch(gemm_tc_kernel<BN>, dim3(blocks), dim3(TC_THREADS), TcConfig<BN>::SMEM, s, ma, mb, a);
+}
+
+static int check_shape(int rowsA, int rowsB, int K) {
+  if (rowsA <= 0 || rowsB <= 0 || K <= 0) return GB_ERR_BAD_ARG;
+  if (K % 8) return GB_ERR_UNSUPPORTED;   // a row pitch must be a multiple of 16 bytes for TMA
+  return 0;
+}
+
+// plan[0] = BN, plan[1] = blocks, plan[2] = scratch floats, plan[3] = counters.
+GB_EXPORT int gb_gemm_tc_plan(int rowsA, int rowsB, int K, int* plan) {
+  int e = check_shape(rowsA, rowsB, K);
+  if (e) return e;
+  TcPlan pl;
+  e = tc_plan(rowsA, rowsB, K, &pl);
+  if (e) return e;
+  plan[0] = pl.bn;
+  plan[1] = pl.blocks;
+  plan[2] = pl.scratch_floats;
+  plan[3] = pl.counters;
+  return 0;
+}
+
+// A [rowsA, K] and B [rowsB, K] bf16, 16-byte aligned; out as TcArgs describes.
+GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, cudaStream_t s) {
+  int e = check_shape(args->rowsA, args->rowsB, args->K);
+  if (e) return e;
+  if (!A || !B || !args->out || !args->scratch || !args->counters || !args->error) return GB_ERR_BAD_ARG;
+  if ((((uintptr_t)A) | ((uintptr_t)B)) & 15) return GB_ERR_BAD_ARG;
+  if (args->silu) return GB_ERR_UNSUPPORTED;
+  TcPlan pl;
+  e = tc_plan(args->rowsA, args->rowsB, args->K, &pl);
+  if (e) return e;
+  CUtensorMap ma, mb;
+  e = make_map(&ma, A, args->rowsA, args->K, TC_BM);
+  if (e) return e;
+  e = make_map(&mb, B, args->rowsB, args->K, pl.bn);
+  if (e) return e;
+  switch (pl.bn) {
+    case 16: return launch<16>(ma, mb, *args, pl.blocks, s);
+    case 32: return launch<32>(ma, mb, *args, pl.blocks, s);
+    case 64: return launch<64>(ma, mb, *args, pl.blocks, s);
+    case 128: return launch<128>(ma, mb, *args, pl.blocks, s);
+    case 256: return launch<256>(ma, mb, *args, pl.blocks, s);
+  }
+  return GB_ERR_UNSUPPORTED;
+}

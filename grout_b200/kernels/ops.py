@@ -379,6 +379,79 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
     return y
 
 
+# ---------------------------------------------------------------- tcgen05 matrix product
+class _TcArgs(ctypes.Structure):
+    _fields_ = [("out", _P), ("scratch", _P), ("counters", _P), ("error", _P), ("rowsA", _I),
+                ("rowsB", _I), ("K", _I), ("ld", _I), ("transpose_out", _I), ("out_f32", _I),
+                ("silu", _I)]
+
+
+_TC_PLANS = {}
+_TC_ERRORS = {}
+_TC_ERROR_NAMES = {101: "the MMA warp waited 2 s for a stage that never arrived",
+                   102: "the TMA producer waited 2 s for a stage that was never released",
+                   103: "the epilogue waited 2 s for an accumulator that was never finished",
+                   104: "the MMA warp waited 2 s for an accumulator that was never drained"}
+
+
+def _tc_error_flag(device) -> torch.Tensor:
+    i = torch.device(device).index or 0
+    if i not in _TC_ERRORS:
+        _TC_ERRORS[i] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _TC_ERRORS[i]
+
+
+def check_kernel_errors() -> None:
+    """Reads the flags that kernels with bounded waits set when a wait expires
+    (this synchronises with the device); raises if any is set."""
+    for i, flag in _TC_ERRORS.items():
+        code = int(flag.item())
+        if code:
+            flag.zero_()
+            raise KernelError(f"gemm_tc on cuda:{i}: {_TC_ERROR_NAMES.get(code, code)}")
+
+
+def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
+                 swap: Optional[bool] = None) -> torch.Tensor:
+    """x [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in
+    tensor memory).  ``swap``: put the weight rows on the 128-row side of the MMA
+    and the activation rows on the narrow side (the layout for few rows); by
+    default chosen when M <= 64."""
+    _need(x, "activations", torch.bfloat16, 2)
+    _need(w, "weight", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"weight is {tuple(w.shape)} for activations of width {K}")
+    if K % 8:
+        raise KernelError(f"gemm_tc_bf16 needs an inner size that is a multiple of 8, got {K}")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"output must be bfloat16 or float32, not {out_dtype}")
+    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if M == 0:
+        return y
+    swap = (M <= 64) if swap is None else bool(swap)
+    A, B = (w, x) if swap else (x, w)
+    with torch.cuda.device(x.device):
+        key = (A.shape[0], B.shape[0], K, torch.cuda.current_device())
+        plan = _TC_PLANS.get(key)
+        if plan is None:
+            out = (c_int * 4)()
+            _check(_fn("gemm_tc", "gb_gemm_tc_plan", "iiip")(
+                A.shape[0], B.shape[0], K, ctypes.addressof(out)), "gemm_tc_plan", 0)
+            plan = _TC_PLANS[key] = (out[0], out[1], out[2], out[3])
+        ws = _WORKSPACES.setdefault(x.device.index or 0, _Workspace())
+        scratch, counters = ws.get(x.device, plan[2], plan[3])
+        a = _TcArgs()
+        a.out, a.scratch, a.counters = y.data_ptr(), scratch.data_ptr(), counters.data_ptr()
+        a.error = _tc_error_flag(x.device).data_ptr()
+        a.rowsA, a.rowsB, a.K, a.ld = A.shape[0], B.shape[0], K, N
+        a.transpose_out, a.out_f32, a.silu = int(swap), int(out_dtype == torch.float32), 0
+        _check(_fn("gemm_tc", "gb_gemm_tc_bf16", "pppp")(
+            A.data_ptr(), B.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc_bf16")
+    return y
+
+
 # ---------------------------------------------------------------- fast bf16 attention
 class _PrefillArgs(ctypes.Structure):
     _fields_ = [("q", _P), ("k_pages", _P), ("v_pages", _P), ("block_table", _P), ("cu_q", _P),

@@ -1,0 +1,56 @@
+"""The tcgen05 matrix product alone against a 64-bit product, in both
+orientations, at sizes with ragged edges, and with tiles shared between blocks."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rand(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16)
+
+
+def _check(M, N, K, out_dtype, swap, seed=0):
+    from grout_b200.kernels import ops
+    x, w = _rand((M, K), 50 + seed), _rand((N, K), 51 + seed, 0.05)
+    got = ops.gemm_tc_bf16(x.to(DEV), w.to(DEV), out_dtype, swap=swap)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    want = x.double() @ w.double().T
+    e = 2.0 ** -8 if out_dtype == torch.bfloat16 else 0.0
+    assert got.shape == (M, N) and got.dtype == out_dtype
+    err = (got.double().cpu() - want).abs()
+    bound = 2e-5 * math.sqrt(K) + 2 * e + 2 * e * want.abs()
+    assert bool((err <= bound).all()), (M, N, K, swap, err.max().item())
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (300, 200, 264), (2048, 512, 2560),
+                                   (70, 1000, 96), (513, 130, 4096)])
+def test_prefill_orientation(M, N, K, out_dtype):
+    _check(M, N, K, out_dtype, swap=False)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 2560, 9728), (16, 6144, 2560), (33, 200, 264),
+                                   (64, 2560, 4096), (5, 19456, 2560)])
+def test_decode_orientation(M, N, K, out_dtype):
+    _check(M, N, K, out_dtype, swap=True)
+
+
+def test_twice_in_a_row_and_row_independence():
+    """Shared tiles leave their counters at zero; a row's result does not depend
+    on the rows beside it when the layout is the same."""
+    from grout_b200.kernels import ops
+    x, w = _rand((16, 4096), 60).to(DEV), _rand((2560, 4096), 61, 0.05).to(DEV)
+    a = ops.gemm_tc_bf16(x, w, torch.float32)
+    b = ops.gemm_tc_bf16(x, w, torch.float32)
+    one = ops.gemm_tc_bf16(x[9:10].contiguous(), w, torch.float32)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    assert torch.equal(a, b)
+    assert torch.equal(a[9:10], one)
