@@ -180,6 +180,7 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
 // per output row, which one block per kv head would have to do alone.
 __global__ void attn_decode_merge_kernel(const float* part_o, const float* part_ml,
                                          bf16* __restrict__ out, int n_splits, int D) {
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const size_t p0 = (size_t)blockIdx.x * n_splits;
   float M = -INFINITY;
@@ -189,7 +190,7 @@ __global__ void attn_decode_merge_kernel(const float* part_o, const float* part_
     const float m = part_ml[(p0 + s) * 2];
     if (m != -INFINITY) L += part_ml[(p0 + s) * 2 + 1] * exp2f(m - M);
   }
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_large();
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float O = 0.f;
     for (int s = 0; s < n_splits; ++s) {

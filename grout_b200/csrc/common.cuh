@@ -85,6 +85,19 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 #endif
 }
 
+// A kernel whose whole grid is resident at once (a handful of blocks) loses
+// nothing by letting its successor in on entry, and the successor (typically a
+// matrix product) can then stream its weights while this kernel runs.
+__device__ __forceinline__ bool pdl_small_grid() {
+  return gridDim.x * gridDim.y * gridDim.z <= 512;
+}
+__device__ __forceinline__ void pdl_launch_dependents_if_small() {
+  if (pdl_small_grid()) pdl_launch_dependents();
+}
+__device__ __forceinline__ void pdl_launch_dependents_if_large() {
+  if (!pdl_small_grid()) pdl_launch_dependents();
+}
+
 static inline bool gb_pdl_enabled() {
   static int on = -1;
   if (on < 0) on = getenv("GROUT_B200_NO_PDL") ? 0 : 1;

@@ -9,6 +9,7 @@
 // (the reference's silu_mul_2d_f16, src/kernels.rs:271-296).
 template <typename T>
 __global__ void silu_mul_kernel(const T* in, T* __restrict__ out, int I, int group) {
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const size_t r = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -17,7 +18,7 @@ __global__ void silu_mul_kernel(const T* in, T* __restrict__ out, int I, int gro
   const int ui = group ? gi + group : I + i;
   const float g = to_f32<T>(in[r * 2 * I + gi]);
   const float u = to_f32<T>(in[r * 2 * I + ui]);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_large();
   out[r * I + i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
 }
 

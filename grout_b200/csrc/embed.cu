@@ -5,6 +5,7 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* ids,
                              T* __restrict__ out, int H, int V) {
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
@@ -20,7 +21,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* ids,
   } else {
     for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? src[i] : from_f32<T>(0.f);
   }
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_large();
 }
 
 template <typename T>

@@ -46,11 +46,13 @@
 
 struct TcArgs {
   void* out;            // [rowsA, ld] or, transposed, [rowsB, ld]
-  float* scratch;       // [2 * blocks][BN][128] partial tiles
+  float* scratch;       // [2 * blocks][128][BN] partial tiles
   unsigned* counters;   // [tiles], zero before the first launch
   int* error;           // device int, 0 while all is well
   int rowsA, rowsB, K, ld;
-  int transpose_out, out_f32, silu;
+  int transpose_out, out_f32;
+  int silu;             // transposed output only: rows of A are gate|up interleaved in eights
+  int dep_b;            // which operand an earlier kernel writes: 1 = B, 0 = A
 };
 
 // ---- PTX wrappers ------------------------------------------------------------
@@ -226,33 +228,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
 
-  pdl_wait();   // activations (and the scratch of an earlier launch) are complete
-
+  // Only the producer lane waits for the kernel before this one (see below): the
+  // MMAs need its loads and the epilogue needs the MMAs, so nothing here reads or
+  // writes global memory before that wait has returned.
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
-      long long it = 0;
-      bool ok = true;
-      for (long long u = u_begin; u < u_end && ok;) {
-        const int tile = (int)(u / kblocks);
-        const int kb_lo = (int)(u - (long long)tile * kblocks);
-        const int kb_hi = (int)min((long long)kblocks, kb_lo + (u_end - u));
-        u += kb_hi - kb_lo;
+      const long long n_units = u_end - u_begin;
+      // The operand that no kernel writes (the weights) is requested for the first
+      // ring of stages before this kernel waits for its producer; the other
+      // operand (the activations) follows once that kernel has finished.
+      const long long n_early = n_units < STAGES ? n_units : STAGES;
+      auto issue = [&](long long it, bool want_a, bool want_b) {
+        const long long u = u_begin + it;
+        const int tile = (int)(u / kblocks), kb = (int)(u - (long long)tile * kblocks);
         const int ta = tile % tiles_a, tb = tile / tiles_a;
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
-          const int s = (int)(it % STAGES);
-          const uint32_t round = (uint32_t)(it / STAGES);
-          if (!mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag)) {
-            if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_TIMEOUT_EMPTY);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          uint8_t* sa = tiles_base + (size_t)s * Cfg::STAGE_BYTES;
-          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
-          tma_load_2d(sa, &map_a, kb * TC_BK, ta * TC_BM, &full[s]);
-          tma_load_2d(sa + Cfg::A_BYTES, &map_b, kb * TC_BK, tb * BN, &full[s]);
+        const int s = (int)(it % STAGES);
+        uint8_t* sa = tiles_base + (size_t)s * Cfg::STAGE_BYTES;
+        if (want_a) tma_load_2d(sa, &map_a, kb * TC_BK, ta * TC_BM, &full[s]);
+        if (want_b) tma_load_2d(sa + Cfg::A_BYTES, &map_b, kb * TC_BK, tb * BN, &full[s]);
+      };
+      for (long long it = 0; it < n_early; ++it) {   // first round: every stage is free
+        mbar_expect_tx(&full[it % STAGES], Cfg::STAGE_BYTES);
+        issue(it, a.dep_b != 0, a.dep_b == 0);
+      }
+      pdl_wait();
+      for (long long it = 0; it < n_early; ++it) issue(it, a.dep_b == 0, a.dep_b != 0);
+      bool ok = true;
+      long long it = n_early;
+      for (; it < n_units; ++it) {
+        const int s = (int)(it % STAGES);
+        const uint32_t round = (uint32_t)(it / STAGES);
+        if (!mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag)) {
+          if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_TIMEOUT_EMPTY);
+          *abort_flag = 1;
+          ok = false;
+          break;
         }
+        mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+        issue(it, true, true);
       }
       pdl_launch_dependents();
       // Every load issued above completes on a `full` barrier that the MMA warp
@@ -335,7 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       bool write_out = whole;
       int p_first = 0, p_last = 0;
       if (!whole) {
-        // leave the partial [BN][128] in this block's slot, then see who is last
+        // leave the partial [128][BN] in this block's slot, then see who is last
         const bool my_first_tile = (int)(u_begin / kblocks) == tile;
         float* mine = a.scratch + ((size_t)2 * p + (my_first_tile ? 0 : 1)) * (size_t)(BN * TC_BM);
 #pragma unroll 1
@@ -343,8 +357,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           uint32_t v[16];
           tc_ld16(taddr + c0, v);
           tc_wait_ld();
+          float4* dst = reinterpret_cast<float4*>(mine + (size_t)r * BN + c0);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * TC_BM + r] = __uint_as_float(v[j]);
+          for (int j = 0; j < 4; ++j)
+            dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                 __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
         }
         tc_fence_before();
         __syncwarp();
@@ -376,16 +393,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) f[j] = 0.f;
-            for (int qb = p_first; qb <= p_last; ++qb) {   // block order: a fixed sum
-              const bool q_first = (int)(((long long)qb * U / P) / kblocks) == tile;
-              const float* src =
-                  a.scratch + ((size_t)2 * qb + (q_first ? 0 : 1)) * (size_t)(BN * TC_BM);
+            // four contributors' rows are requested at once, then added in block
+            // order, so the sum is a fixed one
+            for (int qb = p_first; qb <= p_last; qb += 4) {
+              float4 t[4][4];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) f[j] += __ldcg(src + (size_t)(c0 + j) * TC_BM + r);
+              for (int i = 0; i < 4; ++i) {
+                const int qq = qb + i <= p_last ? qb + i : p_last;
+                const bool q_first = (int)(((long long)qq * U / P) / kblocks) == tile;
+                const float4* src = reinterpret_cast<const float4*>(
+                    a.scratch + ((size_t)2 * qq + (q_first ? 0 : 1)) * (size_t)(BN * TC_BM) +
+                    (size_t)r * BN + c0);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) t[i][k] = __ldcg(src + k);
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                if (qb + i <= p_last) {
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) {
+                    f[4 * k] += t[i][k].x;
+                    f[4 * k + 1] += t[i][k].y;
+                    f[4 * k + 2] += t[i][k].z;
+                    f[4 * k + 3] += t[i][k].w;
+                  }
+                }
+              }
             }
           }
           // store 16 columns of row r
-          if (a.transpose_out) {
+          if (a.transpose_out && a.silu) {
+            // rows 16t..16t+7 of A are gates and 16t+8..16t+15 the matching ups: the up
+            // of this lane's gate sits 8 lanes further; out[col_b][feature] = silu(g) * u
+            // (the reference's silu_mul_2d_f16, src/kernels.rs:271-296, as an epilogue)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float up = __shfl_down_sync(0xffffffffu, f[j], 8);
+              const int cb = tb * BN + c0 + j;
+              if ((lane & 15) < 8 && row_a < a.rowsA && cb < a.rowsB) {
+                const size_t o = (size_t)cb * a.ld + (size_t)(row_a >> 4) * 8 + (row_a & 7);
+                const float val = f[j] / (1.0f + expf(-f[j])) * up;
+                if (a.out_f32) ((float*)a.out)[o] = val;
+                else ((bf16*)a.out)[o] = __float2bfloat16_rn(val);
+              }
+            }
+          } else if (a.transpose_out) {
             // out[col_b][row_a]: lanes hold consecutive row_a, so each j is a coalesced store
             if (row_a < a.rowsA) {
 #pragma unroll
@@ -553,7 +605,7 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   if (e) return e;
   if (!A || !B || !args->out || !args->scratch || !args->counters || !args->error) return GB_ERR_BAD_ARG;
   if ((((uintptr_t)A) | ((uintptr_t)B)) & 15) return GB_ERR_BAD_ARG;
-  if (args->silu) return GB_ERR_UNSUPPORTED;
+  if (args->silu && (!args->transpose_out || (args->rowsA % 16))) return GB_ERR_UNSUPPORTED;
   TcPlan pl;
   e = tc_plan(args->rowsA, args->rowsB, args->K, &pl);
   if (e) return e;

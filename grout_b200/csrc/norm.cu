@@ -17,6 +17,7 @@ __global__ void add_rmsnorm_kernel(const float* res_in, const T* delta,
                                    const int* __restrict__ rows, const WT* __restrict__ w,
                                    float eps, float* res_out, T* __restrict__ y, int N) {
   __shared__ float scratch[32];
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const int r = blockIdx.x;
   const size_t s = rows ? (size_t)rows[r] : (size_t)r;
@@ -30,7 +31,7 @@ __global__ void add_rmsnorm_kernel(const float* res_in, const T* delta,
     ss += v * v;
   }
   ss = block_sum(ss, scratch);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_large();
   const float inv = 1.0f / sqrtf(ss / (float)N + eps);
   T* yo = y + (size_t)r * N;
   for (int i = threadIdx.x; i < N; i += blockDim.x) {
@@ -75,6 +76,7 @@ __global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta,
                                        const int* __restrict__ rows, const WT* __restrict__ w,
                                        float eps, float* res_out, T* __restrict__ y, int N) {
   __shared__ float scratch[32];
+  pdl_launch_dependents_if_small();
   // the weight vector is no kernel's output: fetch it while the producer drains
   float wv[NV_MAX][4];
 #pragma unroll
@@ -106,7 +108,7 @@ __global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta,
     }
   }
   ss = block_sum(ss, scratch);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_large();
   const float inv = 1.0f / sqrtf(ss / (float)N + eps);
   T* yo = y + (size_t)r * N;
 #pragma unroll

@@ -28,6 +28,7 @@ struct QkPrepareArgs {
 template <typename T, typename WT>
 __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
   extern __shared__ float sm[];
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -40,7 +41,7 @@ __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
   const int kind = head < a.nq ? 0 : (head < a.nq + a.nkv ? 1 : 2);
   for (int d = lane; d < D; d += 32) x[d] = to_f32<T>(src[d]);
   __syncwarp();
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_large();
   const WT* w = kind == 0 ? (const WT*)a.q_w : (kind == 1 ? (const WT*)a.k_w : nullptr);
   if (w) {
     float ss = 0.f;

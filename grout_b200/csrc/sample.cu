@@ -63,9 +63,10 @@ __device__ ArgBest block_argmax(const float* row, int V, float mul, ArgBest* sh)
 __global__ void __launch_bounds__(ST) argmax_kernel(const float* logits, int V,
                                                     int* __restrict__ out) {
   __shared__ ArgBest sh[ST / 32];
+  pdl_launch_dependents_if_small();
   pdl_wait();
   const ArgBest r = block_argmax(logits + (size_t)blockIdx.x * V, V, 1.0f, sh);
-  pdl_launch_dependents();
+  pdl_launch_dependents_if_large();
   if (threadIdx.x == 0) out[blockIdx.x] = r.i;
 }
 

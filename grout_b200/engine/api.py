@@ -73,8 +73,7 @@ class Engine:
         self.vocab_size = plan.vocab_size
         self.max_batch = self.cache.max_slots
         self.profile: Optional[StepProfile] = None
-        self.sampler = DeviceSampler(device)
-        kernel_build.compile_modules(self.sampler.kernel_modules())
+        self.sampler = DeviceSampler(device)      # its kernels are compiled when first used
 
     # -- construction --------------------------------------------------------
     @classmethod

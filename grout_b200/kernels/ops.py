@@ -383,7 +383,7 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
 class _TcArgs(ctypes.Structure):
     _fields_ = [("out", _P), ("scratch", _P), ("counters", _P), ("error", _P), ("rowsA", _I),
                 ("rowsB", _I), ("K", _I), ("ld", _I), ("transpose_out", _I), ("out_f32", _I),
-                ("silu", _I)]
+                ("silu", _I), ("dep_b", _I)]
 
 
 _TC_PLANS = {}
@@ -412,11 +412,13 @@ def check_kernel_errors() -> None:
 
 
 def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
-                 swap: Optional[bool] = None) -> torch.Tensor:
+                 swap: Optional[bool] = None, silu_mul: bool = False) -> torch.Tensor:
     """x [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in
     tensor memory).  ``swap``: put the weight rows on the 128-row side of the MMA
     and the activation rows on the narrow side (the layout for few rows); by
-    default chosen when M <= 64."""
+    default chosen when M <= 64.  ``silu_mul`` (with swap): the rows of ``w`` are
+    gate and up rows interleaved in groups of 8 and the result is
+    silu(gate) * up, [M, N / 2]."""
     _need(x, "activations", torch.bfloat16, 2)
     _need(w, "weight", torch.bfloat16, 2)
     M, K = x.shape
@@ -427,10 +429,13 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
         raise KernelError(f"gemm_tc_bf16 needs an inner size that is a multiple of 8, got {K}")
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise KernelError(f"output must be bfloat16 or float32, not {out_dtype}")
-    y = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    swap = (M <= 64) if swap is None else bool(swap)
+    if silu_mul and (not swap or N % 16):
+        raise KernelError("the interleaved gate|up epilogue needs the swapped layout and N % 16 == 0")
+    n_out = N // 2 if silu_mul else N
+    y = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     if M == 0:
         return y
-    swap = (M <= 64) if swap is None else bool(swap)
     A, B = (w, x) if swap else (x, w)
     with torch.cuda.device(x.device):
         key = (A.shape[0], B.shape[0], K, torch.cuda.current_device())
@@ -445,8 +450,9 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
         a = _TcArgs()
         a.out, a.scratch, a.counters = y.data_ptr(), scratch.data_ptr(), counters.data_ptr()
         a.error = _tc_error_flag(x.device).data_ptr()
-        a.rowsA, a.rowsB, a.K, a.ld = A.shape[0], B.shape[0], K, N
-        a.transpose_out, a.out_f32, a.silu = int(swap), int(out_dtype == torch.float32), 0
+        a.rowsA, a.rowsB, a.K, a.ld = A.shape[0], B.shape[0], K, n_out
+        a.transpose_out, a.out_f32 = int(swap), int(out_dtype == torch.float32)
+        a.silu, a.dep_b = int(silu_mul), int(swap)      # the activations are another kernel's output
         _check(_fn("gemm_tc", "gb_gemm_tc_bf16", "pppp")(
             A.data_ptr(), B.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc_bf16")
     return y
@@ -514,9 +520,14 @@ def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, 
     return out
 
 
+DECODE_SPLITS_OVERRIDE: Optional[int] = None      # for experiments
+
+
 def decode_splits(n_seqs: int, nkv: int, max_kv_len: int, device) -> int:
     """How many ways the keys of a sequence are split: enough blocks for about
     three waves of three resident blocks per SM, but at least 128 keys a split."""
+    if DECODE_SPLITS_OVERRIDE:
+        return DECODE_SPLITS_OVERRIDE
     want = (8 * _sm_count(device) + n_seqs * nkv - 1) // (n_seqs * nkv)
     most = max(1, (max_kv_len + 127) // 128)
     return max(1, min(want, most, 64))

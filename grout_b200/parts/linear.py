@@ -5,10 +5,13 @@ It picks the product by the weight's precision and by the number of rows:
 * 32-bit weight: the true 32-bit CUDA-core product (``gemm_f32``); bf16
   activations are widened first and the result narrowed, so a tensor that the
   checkpoint stores in 32-bit is used in 32-bit.
-* bf16 weight, up to 64 rows: the hand-written weight-streaming kernel
-  (``gemm_skinny_bf16``) — every decode step.
-* bf16 weight, more rows: the library's matrix product, which is where the
-  reference uses a library too (cuBLAS GemmEx, src/cublas.rs:287-307).
+* bf16 weight, up to 64 rows (every decode step): the TMA-fed tcgen05 product
+  with the weight rows on the 128-row side of the MMA (``gemm_tc_bf16`` with
+  ``swap``), or, for ``decode_kernel = "skinny"``, the mma.sync weight-streaming
+  kernel (``gemm_skinny_bf16``).
+* bf16 weight, more rows: by default the library's matrix product, which is where
+  the reference uses a library too (cuBLAS GemmEx, src/cublas.rs:287-307); with
+  ``prefill_kernel = "tc"`` the same tcgen05 kernel in its other orientation.
 """
 from __future__ import annotations
 
@@ -20,6 +23,9 @@ from ..kernels import ops
 
 
 class Linear:
+    decode_kernel = "tc"          # "tc" | "skinny": the product for up to 64 rows
+    prefill_kernel = "library"    # "library" | "tc": the product for more rows
+
     def __init__(self, weight: torch.Tensor):
         if weight.dim() != 2:
             raise ValueError(f"a linear weight is [out, in], got {tuple(weight.shape)}")
@@ -31,7 +37,7 @@ class Linear:
     def kernel_modules(self):
         if self.weight.dtype == torch.float32:
             return ("gemm_f32", "elementwise")
-        return ("gemm_skinny_bf16",)
+        return ("gemm_tc", "gemm_skinny_bf16")
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         out_dtype = out_dtype or x.dtype
@@ -42,8 +48,13 @@ class Linear:
         if x.dtype != torch.bfloat16:
             raise ops.KernelError("a bfloat16 weight takes bfloat16 activations")
         M = x.shape[0]
-        if M <= ops.SKINNY_MAX_ROWS and self.in_features % 8 == 0:
-            return ops.gemm_skinny_bf16(x, w, out_dtype)
+        if self.in_features % 8 == 0:
+            if M <= ops.SKINNY_MAX_ROWS:
+                if self.decode_kernel == "tc":
+                    return ops.gemm_tc_bf16(x, w, out_dtype, swap=True)
+                return ops.gemm_skinny_bf16(x, w, out_dtype)
+            if self.prefill_kernel == "tc":
+                return ops.gemm_tc_bf16(x, w, out_dtype, swap=False)
         if out_dtype == torch.float32:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
@@ -55,5 +66,7 @@ class Linear:
         w = self.weight
         if (interleave == 8 and w.dtype == torch.bfloat16 and x.shape[0] <= ops.SKINNY_MAX_ROWS
                 and self.in_features % 8 == 0):
+            if self.decode_kernel == "tc":
+                return ops.gemm_tc_bf16(x, w, x.dtype, swap=True, silu_mul=True)
             return ops.gemm_skinny_bf16(x, w, x.dtype, silu_mul=True)
         return ops.silu_mul(self(x), interleave)

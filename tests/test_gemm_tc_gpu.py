@@ -54,3 +54,19 @@ def test_twice_in_a_row_and_row_independence():
     ops.check_kernel_errors()
     assert torch.equal(a, b)
     assert torch.equal(a[9:10], one)
+
+
+@pytest.mark.parametrize("M", [1, 8, 33, 64])
+@pytest.mark.parametrize("I,K", [(152, 96), (9728, 2560), (24, 4096)])
+def test_silu_epilogue(M, I, K):
+    """Gate and up rows interleaved in groups of 8; the kernel returns silu(gate) * up."""
+    from grout_b200.kernels import ops
+    x = _rand((M, K), 70)
+    gate, up = _rand((I, K), 71, 0.05), _rand((I, K), 72, 0.05)
+    w = torch.stack([gate.view(-1, 8, K), up.view(-1, 8, K)], 1).reshape(2 * I, K).contiguous()
+    got = ops.gemm_tc_bf16(x.to(DEV), w.to(DEV), torch.bfloat16, swap=True, silu_mul=True).cpu()
+    ops.check_kernel_errors()
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    want = g / (1 + torch.exp(-g)) * u
+    assert got.shape == (M, I)
+    assert torch.allclose(got.double(), want, atol=2e-4, rtol=3 * 2.0 ** -8)
