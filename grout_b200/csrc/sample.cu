@@ -60,20 +60,68 @@ __device__ ArgBest block_argmax(const float* row, int V, float mul, ArgBest* sh)
   return r;
 }
 
-__global__ void __launch_bounds__(ST) argmax_kernel(const float* logits, int V,
-                                                    int* __restrict__ out) {
-  __shared__ ArgBest sh[ST / 32];
+// Stage 1: block (chunk, row) finds the first maximum of its slice of the row.
+// Stage 2: one warp per row picks the first maximum among the chunks.  Two short
+// launches instead of one block per row, which left most of the GPU idle.
+#define ARGMAX_CHUNKS 32
+
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits, int V,
+                                                             float* part_v, int* part_i) {
+  __shared__ ArgBest sh[8];
   pdl_launch_dependents_if_small();
   pdl_wait();
-  const ArgBest r = block_argmax(logits + (size_t)blockIdx.x * V, V, 1.0f, sh);
-  pdl_launch_dependents_if_large();
-  if (threadIdx.x == 0) out[blockIdx.x] = r.i;
+  const int row = blockIdx.y, chunk = blockIdx.x;
+  const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+  const int lo = chunk * per, hi = min(V, lo + per);
+  const float* r = logits + (size_t)row * V;
+  ArgBest best{-INFINITY, INT_MAX};
+  for (int i = lo + threadIdx.x; i < hi; i += 256) {
+    float v = r[i];
+    if (v != v) v = -INFINITY;
+    if (v > best.v || (v == best.v && i < best.i)) best = ArgBest{v, i};
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ArgBest b = sh[0];
+    for (int w = 1; w < 8; ++w) b = better(b, sh[w]);
+    part_v[row * ARGMAX_CHUNKS + chunk] = b.v;
+    part_i[row * ARGMAX_CHUNKS + chunk] = b.i;
+  }
 }
 
-GB_EXPORT int gb_argmax_f32(const float* logits, int n_rows, int V, int* out, cudaStream_t s) {
-  if (n_rows < 0 || V <= 0) return GB_ERR_BAD_ARG;
+__global__ void __launch_bounds__(32) argmax_final_kernel(const float* part_v, const int* part_i,
+                                                          int* out) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int row = blockIdx.x;
+  ArgBest best{part_v[row * ARGMAX_CHUNKS + threadIdx.x], part_i[row * ARGMAX_CHUNKS + threadIdx.x]};
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgBest other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, other);
+  }
+  if (threadIdx.x == 0) out[row] = best.i == INT_MAX ? 0 : best.i;
+}
+
+// scratch: n_rows * 32 floats followed by n_rows * 32 ints (the caller's).
+GB_EXPORT int gb_argmax_f32(const float* logits, int n_rows, int V, int* out, void* scratch,
+                            cudaStream_t s) {
+  if (n_rows < 0 || V <= 0 || !scratch) return GB_ERR_BAD_ARG;
   if (n_rows == 0) return 0;
-  return gb_launch(argmax_kernel, dim3(n_rows), dim3(ST), 0, s, logits, V, out);
+  if (n_rows > 65535) return GB_ERR_UNSUPPORTED;
+  float* pv = (float*)scratch;
+  int* pi = (int*)(pv + (size_t)n_rows * ARGMAX_CHUNKS);
+  int e = gb_launch(argmax_partial_kernel, dim3(ARGMAX_CHUNKS, n_rows), dim3(256), 0, s, logits, V,
+                    pv, pi);
+  if (e) return e;
+  return gb_launch(argmax_final_kernel, dim3(n_rows), dim3(32), 0, s, (const float*)pv,
+                   (const int*)pi, out);
 }
 
 // ---------------------------------------------------------------------------

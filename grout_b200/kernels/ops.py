@@ -524,13 +524,20 @@ DECODE_SPLITS_OVERRIDE: Optional[int] = None      # for experiments
 
 
 def decode_splits(n_seqs: int, nkv: int, max_kv_len: int, device) -> int:
-    """How many ways the keys of a sequence are split: enough blocks for about
-    three waves of three resident blocks per SM, but at least 128 keys a split."""
+    """How many ways the keys of a sequence are split.  Blocks run in waves of
+    three per SM; with S splits a block streams 1/S of a sequence's 32-key tiles
+    plus a fixed cost of about three tiles (query load, merge, partial store), so
+    the step costs waves(S) * (tiles / S + 3).  The smallest S within 3 % of the
+    cheapest is taken, with at least 256 keys a split."""
     if DECODE_SPLITS_OVERRIDE:
         return DECODE_SPLITS_OVERRIDE
-    want = (8 * _sm_count(device) + n_seqs * nkv - 1) // (n_seqs * nkv)
-    most = max(1, (max_kv_len + 127) // 128)
-    return max(1, min(want, most, 64))
+    slots = 3 * _sm_count(device)
+    pairs = max(1, n_seqs * nkv)
+    tiles = max(1, (max_kv_len + 31) // 32)
+    most = max(1, min(64, (max_kv_len + 255) // 256))
+    cost = {s: ((pairs * s + slots - 1) // slots) * (tiles / s + 3.0) for s in range(1, most + 1)}
+    best = min(cost.values())
+    return min(s for s, c in cost.items() if c <= 1.03 * best)
 
 
 def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: int, scale: float,
@@ -594,8 +601,10 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     """First maximum of every row of 32-bit logits -> int32 [rows]."""
     _need(logits, "logits", torch.float32, 2)
     out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
-    _check(_fn("sample", "gb_argmax_f32", "piipp")(
-        logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(), _stream()), "argmax")
+    scratch = torch.empty((logits.shape[0], 64), dtype=torch.float32, device=logits.device)
+    _check(_fn("sample", "gb_argmax_f32", "piippp")(
+        logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(), scratch.data_ptr(),
+        _stream()), "argmax", 2)
     return out
 
 
