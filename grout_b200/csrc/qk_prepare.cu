@@ -84,6 +84,127 @@ __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
   }
 }
 
+// The same work for bf16 heads whose size is a multiple of 64 and that are
+// rotated whole (or not at all): a lane keeps its 4 * P elements (pairs 2l, 2l+1
+// of each 64-element run, in both halves of the head) in registers, so there is
+// no staging in shared memory and all traffic is in 4-byte pieces.
+template <typename WT, int P>
+__global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
+  pdl_launch_dependents_if_small();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int n_heads = a.nq + 2 * a.nkv;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (head >= n_heads) return;
+  constexpr int D = 64 * P, HALF = D / 2;
+  const bf16* src = (const bf16*)a.qkv + ((size_t)t * n_heads + head) * D;
+  const int kind = head < a.nq ? 0 : (head < a.nq + a.nkv ? 1 : 2);
+  // element index of this lane's p-th pair inside a half: 2 * lane + 64 * p  (< HALF)
+  float lo[P][2], hi[P][2];
+  constexpr int NP = (P + 1) / 2;   // pairs per half per lane: HALF / 64 rounded up
+  // HALF = 32 P elements per half; a lane takes pairs at 2 * lane + 64 * p while inside it
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    const int j = 2 * lane + 64 * p;
+    if (j < HALF) {
+      const __nv_bfloat162 l2 = *reinterpret_cast<const __nv_bfloat162*>(src + j);
+      const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(src + HALF + j);
+      lo[p][0] = __low2float(l2); lo[p][1] = __high2float(l2);
+      hi[p][0] = __low2float(h2); hi[p][1] = __high2float(h2);
+    } else {
+      lo[p][0] = lo[p][1] = hi[p][0] = hi[p][1] = 0.f;
+    }
+  }
+  pdl_launch_dependents_if_large();
+  const WT* w = kind == 0 ? (const WT*)a.q_w : (kind == 1 ? (const WT*)a.k_w : nullptr);
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int p = 0; p < NP; ++p)
+      ss += lo[p][0] * lo[p][0] + lo[p][1] * lo[p][1] + hi[p][0] * hi[p][0] + hi[p][1] * hi[p][1];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const int j = 2 * lane + 64 * p;
+      if (j < HALF) {
+        lo[p][0] = lo[p][0] * inv * to_f32<WT>(w[j]);
+        lo[p][1] = lo[p][1] * inv * to_f32<WT>(w[j + 1]);
+        hi[p][0] = hi[p][0] * inv * to_f32<WT>(w[HALF + j]);
+        hi[p][1] = hi[p][1] * inv * to_f32<WT>(w[HALF + j + 1]);
+      }
+    }
+  }
+  const int pos = a.token_pos[t];
+  if (kind != 2 && a.inv_freq) {
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const int j = 2 * lane + 64 * p;
+      if (j < HALF) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float angle = (float)pos * a.inv_freq[j + e];
+          float sn, cs;
+          sincosf(angle, &sn, &cs);
+          const float l = lo[p][e], h = hi[p][e];
+          lo[p][e] = l * cs - h * sn;
+          hi[p][e] = h * cs + l * sn;
+        }
+      }
+    }
+  }
+  bf16* dst = nullptr;
+  bf16* dst2 = nullptr;
+  if (kind == 0) {
+    dst = (bf16*)a.q_out + ((size_t)t * a.nq + head) * D;
+  } else {
+    const int hh = kind == 1 ? head - a.nq : head - a.nq - a.nkv;
+    if (a.kv_out)
+      dst2 = (bf16*)a.kv_out + ((size_t)t * 2 * a.nkv + (kind == 1 ? hh : a.nkv + hh)) * D;
+    if (a.k_pages) {
+      const int slot = a.slots[a.token_seq[t]];
+      if (slot >= 0) {
+        const int* table = a.block_table + (size_t)slot * a.max_pages;
+        dst = (bf16*)(kind == 1 ? a.k_pages : a.v_pages) + paged_row(table, pos, hh, a.nkv, a.page, D);
+      }
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    const int j = 2 * lane + 64 * p;
+    if (j < HALF) {
+      const __nv_bfloat162 l2 = __floats2bfloat162_rn(lo[p][0], lo[p][1]);
+      const __nv_bfloat162 h2 = __floats2bfloat162_rn(hi[p][0], hi[p][1]);
+      if (dst) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + j) = l2;
+        *reinterpret_cast<__nv_bfloat162*>(dst + HALF + j) = h2;
+      }
+      if (dst2) {
+        *reinterpret_cast<__nv_bfloat162*>(dst2 + j) = l2;
+        *reinterpret_cast<__nv_bfloat162*>(dst2 + HALF + j) = h2;
+      }
+    }
+  }
+}
+
+template <typename WT>
+static int launch_fast(const QkPrepareArgs& a, cudaStream_t stream) {
+  const int warps = 4;
+  const int n_heads = a.nq + 2 * a.nkv;
+  dim3 grid(a.n_tokens, (n_heads + warps - 1) / warps);
+  switch (a.D / 64) {
+    case 1: return gb_launch(qk_prepare_fast_kernel<WT, 1>, grid, dim3(warps * 32), 0, stream, a);
+    case 2: return gb_launch(qk_prepare_fast_kernel<WT, 2>, grid, dim3(warps * 32), 0, stream, a);
+    case 4: return gb_launch(qk_prepare_fast_kernel<WT, 4>, grid, dim3(warps * 32), 0, stream, a);
+  }
+  return GB_ERR_UNSUPPORTED;
+}
+
+static bool fast_ok(const QkPrepareArgs& a) {
+  return (a.D == 64 || a.D == 128 || a.D == 256) && (!a.inv_freq || a.rot_dim == a.D);
+}
+
 template <typename T, typename WT>
 static int launch(const QkPrepareArgs& a, cudaStream_t stream) {
   const int warps = 4;
@@ -115,6 +236,7 @@ GB_EXPORT int gb_qk_prepare_bf16(const QkPrepareArgs* a, int w_is_f32, cudaStrea
   int e = check(*a);
   if (e) return e;
   if (a->n_tokens == 0) return 0;
+  if (fast_ok(*a)) return w_is_f32 ? launch_fast<float>(*a, s) : launch_fast<bf16>(*a, s);
   return w_is_f32 ? launch<bf16, float>(*a, s) : launch<bf16, bf16>(*a, s);
 }
 

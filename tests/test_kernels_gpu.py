@@ -159,7 +159,8 @@ def test_attn_generic(dtype, nq, nkv, D, window):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
-@pytest.mark.parametrize("nq,nkv,D,rot", [(6, 2, 48, 48), (4, 4, 64, 32), (8, 1, 128, 128)])
+@pytest.mark.parametrize("nq,nkv,D,rot", [(6, 2, 48, 48), (4, 4, 64, 32), (8, 1, 128, 128),
+                                          (3, 3, 64, 64), (2, 1, 256, 256), (4, 2, 128, 64)])
 def test_qk_prepare(dtype, nq, nkv, D, rot):
     dt = DT[dtype]
     theta, eps = 50000.0, 1e-5
@@ -308,6 +309,17 @@ def test_silu_mul_and_cast(dtype):
     g, u = gu.double()[:, :301], gu.double()[:, 301:]
     want = g / (1 + torch.exp(-g)) * u
     assert torch.allclose(got.double(), want, atol=2 * _eps(dt), rtol=2 * _eps(dt))
+    # widths in whole runs of 8 take the 16-byte path (bf16), plain and interleaved
+    for I, group in ((304, 0), (304, 8), (9728, 8)):
+        gu = _rand((5, 2 * I), dt, 32 + I + group, 3.0)
+        got = _ops().silu_mul(gu.to(DEV), group).cpu()
+        if group:
+            v = gu.double().view(5, -1, 2, group)
+            g, u = v[:, :, 0].reshape(5, I), v[:, :, 1].reshape(5, I)
+        else:
+            g, u = gu.double()[:, :I], gu.double()[:, I:]
+        want = g / (1 + torch.exp(-g)) * u
+        assert torch.allclose(got.double(), want, atol=2 * _eps(dt), rtol=2 * _eps(dt)), (I, group)
     x = _rand((1000,), torch.float32, 31)
     assert torch.equal(_ops().cast(x.to(DEV), torch.bfloat16).cpu(), x.to(torch.bfloat16))
     assert torch.equal(_ops().cast(x.to(torch.bfloat16).to(DEV), torch.float32).cpu(),
