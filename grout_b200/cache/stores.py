@@ -3,8 +3,8 @@
 ``KVStore``: keys and values in pages of ``PAGE_TOKENS`` tokens,
 ``[layers, pages, kv heads, PAGE_TOKENS, head_dim]``, with one block table
 ``[slots, pages per sequence]`` shared by the group's layers.  Pointers never
-change after construction, so a captured CUDA graph stays valid.  Nothing is
-zeroed: a sequence's length gates every read.  (The reference keeps one
+change after construction, so a captured CUDA graph stays valid.  Pages are
+zero-filled once and never cleared again: a sequence's length gates every read.  (The reference keeps one
 ``[kv heads, S, D]`` pair per layer for its single sequence,
 src/model.rs:1450-1455.)  A store with a window gives pages back as soon as
 every token in them has left the window of all later queries.
@@ -59,8 +59,11 @@ class KVStore:
         self.k = self.v = self.table_dev = None
         if allocate:
             shape = (n_layers, max(n_pages, 1), spec.n_kv_heads, PAGE_TOKENS, spec.head_dim)
-            self.k = torch.empty(shape, dtype=dtype, device=self.device)
-            self.v = torch.empty(shape, dtype=dtype, device=self.device)
+            # zero-filled once: rows beyond a sequence's length are masked by every
+            # kernel, but a tensor-core product of probability 0 with a NaN that
+            # happened to be in fresh memory would still be NaN
+            self.k = torch.zeros(shape, dtype=dtype, device=self.device)
+            self.v = torch.zeros(shape, dtype=dtype, device=self.device)
             self.table_dev = torch.zeros((max_slots, max_pages_per_seq), dtype=torch.int32,
                                          device=self.device)
 

@@ -388,7 +388,8 @@ class _TcArgs(ctypes.Structure):
 
 _TC_PLANS = {}
 _TC_ERRORS = {}
-_TC_ERROR_NAMES = {101: "the MMA warp waited 2 s for a stage that never arrived",
+_TC_ERROR_NAMES = {111: "a role of the tcgen05 attention kernel waited 2 s on a barrier",
+                   101: "the MMA warp waited 2 s for a stage that never arrived",
                    102: "the TMA producer waited 2 s for a stage that was never released",
                    103: "the epilogue waited 2 s for an accumulator that was never finished",
                    104: "the MMA warp waited 2 s for an accumulator that was never drained"}
@@ -408,7 +409,7 @@ def check_kernel_errors() -> None:
         code = int(flag.item())
         if code:
             flag.zero_()
-            raise KernelError(f"gemm_tc on cuda:{i}: {_TC_ERROR_NAMES.get(code, code)}")
+            raise KernelError(f"tensor-memory kernel on cuda:{i}: {_TC_ERROR_NAMES.get(code, code)}")
 
 
 def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
@@ -475,7 +476,9 @@ class _DecodeArgs(ctypes.Structure):
 
 _LOG2E = 1.4426950408889634
 PREFILL_ROWS = 64          # query rows per block of the prefill kernel
-FAST_ATTENTION_MODULES: Tuple[str, ...] = ("attn_prefill_bf16", "attn_decode_bf16")
+FAST_ATTENTION_MODULES: Tuple[str, ...] = ("attn_prefill_tc", "attn_prefill_bf16",
+                                            "attn_decode_bf16")
+PREFILL_ATTENTION = "tc"      # "tc": tcgen05 where the shape allows; "mma": the mma.sync kernel
 _SM_COUNT = {}
 
 
@@ -517,6 +520,50 @@ def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, 
     a.scale_log2 = float(scale) * _LOG2E
     _check(_fn("attn_prefill_bf16", "gb_attn_prefill_bf16", "piip")(
         ctypes.addressof(a), D, page, _stream()), "attn_prefill_bf16")
+    return out
+
+
+class _AttnTcArgs(ctypes.Structure):
+    _fields_ = [("block_table", _P), ("cu_q", _P), ("slots", _P), ("kv_len", _P), ("out", _P),
+                ("error", _P), ("n_seqs", _I), ("nq", _I), ("nkv", _I), ("max_pages", _I),
+                ("window", _I), ("n_qblocks", _I), ("scale_log2", _F)]
+
+
+PREFILL_TC_ROWS = 128      # query rows per block of the tcgen05 prefill kernel
+
+
+def attn_prefill_tc_takes(D: int, nq: int, nkv: int, page: int) -> bool:
+    return D in (64, 128) and page == 64 and nq % nkv == 0
+
+
+def attn_prefill_tc(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens, page: int,
+                    scale: float, window: Optional[int] = None) -> torch.Tensor:
+    """Causal attention of whole prompts (or their continuation) with both
+    products on the tcgen05 tensor cores.  Pages must hold finite values in the
+    rows beyond a sequence's length (the cache zero-fills its pages)."""
+    _need(q, "q", torch.bfloat16, 3)
+    T, nq, D = q.shape
+    _need(k_pages, "k pages", torch.bfloat16, 4)
+    _need(v_pages, "v pages", torch.bfloat16, 4)
+    nkv = k_pages.shape[1]
+    if tuple(k_pages.shape[1:]) != (nkv, page, D) or v_pages.shape != k_pages.shape:
+        raise KernelError(f"pages are {tuple(k_pages.shape)}, expected [*, nkv, {page}, {D}]")
+    for t, nm in ((block_table, "block table"), (cu_q, "cu_q"), (slots, "slots"), (kv_len, "kv_len")):
+        _need(t, nm, torch.int32)
+    if sum(q_lens) != T or len(q_lens) != slots.shape[0]:
+        raise KernelError("q_lens do not describe the step's rows")
+    out = torch.empty_like(q)
+    a = _AttnTcArgs()
+    a.block_table, a.cu_q, a.slots, a.kv_len = (block_table.data_ptr(), cu_q.data_ptr(),
+                                                slots.data_ptr(), kv_len.data_ptr())
+    a.out, a.error = out.data_ptr(), _tc_error_flag(q.device).data_ptr()
+    a.n_seqs, a.nq, a.nkv, a.max_pages = len(q_lens), nq, nkv, block_table.shape[1]
+    a.window = int(window or 0)
+    a.n_qblocks = sum((n + PREFILL_TC_ROWS - 1) // PREFILL_TC_ROWS for n in q_lens)
+    a.scale_log2 = float(scale) * _LOG2E
+    _check(_fn("attn_prefill_tc", "gb_attn_prefill_tc", "ppppiliip")(
+        q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), ctypes.addressof(a), T,
+        k_pages.shape[0], D, page, _stream()), "attn_prefill_tc")
     return out
 
 
@@ -587,6 +634,11 @@ def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float
             return attn_decode_bf16(q, k_pages, v_pages, block_table, slots=step.slots,
                                     kv_len=step.kv_len, page=page, scale=scale,
                                     max_kv_len=step.max_kv_len, window=window)
+        if step.q_lens and PREFILL_ATTENTION == "tc" and \
+                attn_prefill_tc_takes(D, nq, k_pages.shape[1], page):
+            return attn_prefill_tc(q, k_pages, v_pages, block_table, cu_q=step.cu_q,
+                                   slots=step.slots, kv_len=step.kv_len, q_lens=step.q_lens,
+                                   page=page, scale=scale, window=window)
         if step.q_lens:
             return attn_prefill_bf16(q, k_pages, v_pages, block_table, cu_q=step.cu_q,
                                      slots=step.slots, kv_len=step.kv_len, q_lens=step.q_lens,

@@ -75,7 +75,7 @@ def test_add_rmsnorm(dtype, N, w32):
 class Paged:
     """Sequences laid out in scattered pages, with the dense copies for the oracle."""
 
-    def __init__(self, lens, nkv, D, dtype, seed, page=64, spare=5):
+    def __init__(self, lens, nkv, D, dtype, seed, page=64, spare=5, fill=float("nan")):
         g = torch.Generator().manual_seed(seed)
         self.page, self.nkv, self.D = page, nkv, D
         n_need = sum((n + page - 1) // page for n in lens)
@@ -86,8 +86,8 @@ class Paged:
         self.n_slots = len(lens) + 2
         self.slot_of = torch.randperm(self.n_slots, generator=g).tolist()[:len(lens)]
         self.table = torch.zeros((self.n_slots, self.max_pages), dtype=torch.int32)
-        self.k_pages = torch.full((n_pages, nkv, page, D), float("nan")).to(dtype)
-        self.v_pages = torch.full((n_pages, nkv, page, D), float("nan")).to(dtype)
+        self.k_pages = torch.full((n_pages, nkv, page, D), fill).to(dtype)
+        self.v_pages = torch.full((n_pages, nkv, page, D), fill).to(dtype)
         self.k, self.v = [], []
         for i, n in enumerate(lens):
             k = (torch.randn((n, nkv, D), generator=g)).to(dtype)
@@ -418,3 +418,49 @@ def test_fast_attention_refuses_what_it_cannot_do():
                              slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
                              kv_len=torch.tensor([5], dtype=torch.int32, device=DEV), page=64,
                              scale=1.0, max_kv_len=64)
+
+
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("nq,nkv,D", [(8, 1, 128), (6, 2, 64), (16, 4, 128)])
+def test_attn_prefill_tc(nq, nkv, D, window):
+    """Both products on the tcgen05 tensor cores.  Rows beyond a sequence's length
+    hold large finite values here (the cache zero-fills; NaN there is excluded by
+    the kernel's contract)."""
+    ops = _ops()
+    dt = torch.bfloat16
+    plan = [(0, 1), (0, 130), (37, 100), (64, 64), (0, 300), (5, 63), (100, 200)]
+    lens = [s + n for s, n in plan]
+    pc = Paged(lens, nkv, D, dt, 46, fill=300.0)
+    q_lens = [n for _, n in plan]
+    T = sum(q_lens)
+    q = _rand((T, nq, D), dt, 47)
+    scale = 1.0 / math.sqrt(D)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    if window is None:
+        seq, key, row = 4, 3, cu[4] + 299
+        q[row] = 0
+        q[row, :, 0] = 30.0
+        pc.k[seq][:, :, 0] = 0
+        pc.k[seq][key, :, 0] = 30.0
+        for j in range(lens[seq]):
+            pc.store(seq, j, pc.k[seq][j], pc.v[seq][j])
+    got = ops.attn_prefill_tc(
+        q.to(DEV), pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV),
+        cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+        slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
+        kv_len=torch.tensor(lens, dtype=torch.int32, device=DEV), q_lens=tuple(q_lens), page=64,
+        scale=scale, window=window).cpu()
+    ops.check_kernel_errors()
+    assert not torch.isnan(got.float()).any()
+    for s, (start, n) in enumerate(plan):
+        for i in sorted(set([0, n // 2, n - 1, min(n - 1, 63), min(n - 1, 64), min(n - 1, 127), min(n - 1, 128)])):
+            want = _attn_oracle(q[cu[s] + i], pc.k[s], pc.v[s], start + i, scale, window)
+            assert torch.allclose(got[cu[s] + i].double(), want, **FAST_TOL), (s, i)
+    s, (start, n) = 2, plan[2]
+    for i in range(n):
+        want = _attn_oracle(q[cu[s] + i], pc.k[s], pc.v[s], start + i, scale, window)
+        assert torch.allclose(got[cu[s] + i].double(), want, **FAST_TOL), (s, i)
+    if window is None:
+        assert torch.allclose(got[cu[4] + 299, 0].double(), pc.v[4][3, 0].double(), atol=1e-2, rtol=1e-2)
