@@ -62,6 +62,12 @@ __device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t saddr, uint32_t l
   return d;
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {   // 2^x, one MUFU operation; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int DS>   // head_dim = 64 * DS
 struct AtConfig {
   static constexpr int D = 64 * DS;
@@ -263,12 +269,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (!wait_warp(&r_full[b], ((uint32_t)(i >> 1)) & 1)) return false;
       tc_fence_after();
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 16) {
-        uint32_t v[16];
-        tc_ld16(lane_addr + Cfg::TMEM_R + b * D + c0, v);
+      for (int c0 = 0; c0 < D; c0 += 64) {   // 64 columns per load, one wait per load
+        uint32_t v[64];
+        tc_ld64(lane_addr + Cfg::TMEM_R + b * D + c0, v);
         tc_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[c0 + j] = o[c0 + j] * corr + __uint_as_float(v[j]);
+        for (int j = 0; j < 64; ++j) o[c0 + j] = o[c0 + j] * corr + __uint_as_float(v[j]);
       }
       tc_fence_before();
       __syncwarp();
@@ -281,39 +287,47 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (!wait_warp(&s_full[b], ((uint32_t)(j >> 1)) & 1)) { ok = false; break; }
       tc_fence_after();
       float s[AT_BN];
-#pragma unroll
-      for (int c0 = 0; c0 < AT_BN; c0 += 16) {
-        uint32_t v[16];
-        tc_ld16(lane_addr + Cfg::TMEM_S + b * AT_BN + c0, v);
+      {
+        uint32_t v[AT_BN];
+        tc_ld64(lane_addr + Cfg::TMEM_S + b * AT_BN, v);   // the whole row at once
         tc_wait_ld();
 #pragma unroll
-        for (int jj = 0; jj < 16; ++jj) s[c0 + jj] = __uint_as_float(v[jj]);
+        for (int jj = 0; jj < AT_BN; ++jj) s[jj] = __uint_as_float(v[jj]);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[b]);   // S_j is in registers: the buffer is free
 
       const int key0 = (tile_lo + j) * AT_BN;
-      float mx = -INFINITY;
+      // a tile that lies wholly at or below the block's first position (and inside
+      // every row's window) needs no mask
+      const bool need_mask = key0 + AT_BN - 1 > pos0 || a.window > 0 || rows < AT_BM;
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < AT_BN; ++c) {
-        const int key = key0 + c;
-        const float v = (key < lo || key > hi) ? -INFINITY : s[c] * a.scale_log2;
-        s[c] = v;
-        mx = fmaxf(mx, v);
+        for (int c = 0; c < AT_BN; ++c) {
+          const int key = key0 + c;
+          if (key < lo || key > hi) s[c] = -INFINITY;
+        }
       }
+      // row maximum of the raw scores (the scale is positive), four chains
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < AT_BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
       const float m_new = fmaxf(m, mx);
       const float mbase = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = (m == -INFINITY) ? 0.f : exp2f(m - mbase);
+      const float corr = (m == -INFINITY) ? 0.f : fast_exp2(m - mbase);
       m = m_new;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[AT_BN / 2];
 #pragma unroll
       for (int c = 0; c < AT_BN; c += 2) {
-        const float e0 = exp2f(s[c] - mbase), e1 = exp2f(s[c + 1] - mbase);
-        sum += e0 + e1;
+        const float e0 = fast_exp2(fmaf(s[c], a.scale_log2, -mbase));
+        const float e1 = fast_exp2(fmaf(s[c + 1], a.scale_log2, -mbase));
+        sum4[(c >> 1) & 3] += e0 + e1;
         pk[c / 2] = pack2(e0, e1);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l = l * corr + sum;
 
       // P_j into shared memory, K-major [128 rows][64 keys] under the 128-byte swizzle

@@ -43,8 +43,15 @@ TINY = {
               num_key_value_heads=3, head_dim=48, rope_theta=500000.0, rms_norm_eps=3e-6,
               max_position_embeddings=320, tie_word_embeddings=False, use_sliding_window=True,
               sliding_window=40, max_window_layers=1, eos_token_id=330),
+    # heads of 64: the shapes that the tensor-memory attention and the register-resident
+    # q/k preparation take
+    "D": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=200,
+              hidden_size=128, intermediate_size=192, num_hidden_layers=2, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=64, rope_theta=20000.0, rms_norm_eps=2e-6,
+              max_position_embeddings=512, tie_word_embeddings=True, use_sliding_window=False,
+              eos_token_id=199),
 }
-SEEDS = {"A": 0, "B": 2, "C": 4}
+SEEDS = {"A": 0, "B": 2, "C": 4, "D": 6}
 
 
 @pytest.fixture(scope="session")
