@@ -20,7 +20,9 @@
 // in the softmax.
 //
 // Warps: 0 = TMA producer (one lane), 1 = TMEM allocation and MMA issue (one
-// lane), 2-5 = softmax / accumulation / store (thread = query row).
+// lane), 2-9 = softmax / accumulation / store: two threads per query row, each
+// with half of a tile's keys and half of head_dim, so that every scheduler of the
+// SM holds two such warps.
 //
 // Pages must hold finite values in rows beyond a sequence's length (the cache is
 // zero-filled when it is made): those keys are masked to probability 0, and
@@ -31,7 +33,7 @@
 
 #define AT_BM 128
 #define AT_BN 64
-#define AT_THREADS 192
+#define AT_THREADS 320
 #define AT_STAGES 3
 
 #define GB_ERR_AT_TIMEOUT 111
@@ -109,6 +111,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* r_empty = r_full + 2;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ float xch[6 * AT_BM];   // halves of row maxima (2 tiles x 2 groups) and of l
   volatile int* abort_flag = &abort_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -151,11 +154,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
-      mbar_init(&p_full[i], 4);
+      mbar_init(&s_empty[i], 8);   // one arrival per softmax warp
+      mbar_init(&p_full[i], 8);
       mbar_init(&p_empty[i], 1);
       mbar_init(&r_full[i], 1);
-      mbar_init(&r_empty[i], 4);
+      mbar_init(&r_empty[i], 8);
     }
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -247,15 +250,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
   } else {
     // ------------------------------------------------------------------ softmax, accumulate, store
-    const int q = warp & 3;
+    // Two threads share a query row: group 0 (warps 2-5) owns key columns 0-31 of
+    // every tile and the first half of head_dim, group 1 (warps 6-9) the rest.  The
+    // halves of a row's maximum meet in shared memory once per tile.
+    constexpr int HC = AT_BN / 2, HD = D / 2;
+    const int grp = (warp - 2) >> 2;
+    const int q = warp & 3;                        // the TMEM lanes this warp may read
     const int r = q * 32 + lane;                   // query row of the block
     const int pos = pos0 + r;
     const int hi = r < rows ? pos : -1;            // rows beyond the block see nothing
     const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    float o[D];
+    float o[HD];
 #pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.f;
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
     float m = -INFINITY, l = 0.f, corr_prev = 0.f;
     bool ok = true;
 
@@ -264,18 +272,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (lane == 0) got = mbar_wait(bar, parity, nullptr) ? 1 : 0;
       return __shfl_sync(0xffffffffu, got, 0) != 0;
     };
-    auto accumulate = [&](int i, float corr) -> bool {   // O = O corr + R_i
+    auto accumulate = [&](int i, float corr) -> bool {   // O = O corr + R_i, this group's half
       const int b = i & 1;
       if (!wait_warp(&r_full[b], ((uint32_t)(i >> 1)) & 1)) return false;
       tc_fence_after();
+      uint32_t v[HD];
+      if constexpr (HD == 64) tc_ld64(lane_addr + Cfg::TMEM_R + b * D + grp * HD, v);
+      else tc_ld32(lane_addr + Cfg::TMEM_R + b * D + grp * HD, v);
+      tc_wait_ld();
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 64) {   // 64 columns per load, one wait per load
-        uint32_t v[64];
-        tc_ld64(lane_addr + Cfg::TMEM_R + b * D + c0, v);
-        tc_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 64; ++j) o[c0 + j] = o[c0 + j] * corr + __uint_as_float(v[j]);
-      }
+      for (int j = 0; j < HD; ++j) o[j] = o[j] * corr + __uint_as_float(v[j]);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&r_empty[b]);
@@ -286,25 +292,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int b = j & 1;
       if (!wait_warp(&s_full[b], ((uint32_t)(j >> 1)) & 1)) { ok = false; break; }
       tc_fence_after();
-      float s[AT_BN];
+      float s[HC];
       {
-        uint32_t v[AT_BN];
-        tc_ld64(lane_addr + Cfg::TMEM_S + b * AT_BN, v);   // the whole row at once
+        uint32_t v[HC];
+        tc_ld32(lane_addr + Cfg::TMEM_S + b * AT_BN + grp * HC, v);
         tc_wait_ld();
 #pragma unroll
-        for (int jj = 0; jj < AT_BN; ++jj) s[jj] = __uint_as_float(v[jj]);
+        for (int jj = 0; jj < HC; ++jj) s[jj] = __uint_as_float(v[jj]);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[b]);   // S_j is in registers: the buffer is free
 
-      const int key0 = (tile_lo + j) * AT_BN;
+      const int key0 = (tile_lo + j) * AT_BN + grp * HC;
       // a tile that lies wholly at or below the block's first position (and inside
       // every row's window) needs no mask
-      const bool need_mask = key0 + AT_BN - 1 > pos0 || a.window > 0 || rows < AT_BM;
+      const bool need_mask = (tile_lo + j) * AT_BN + AT_BN - 1 > pos0 || a.window > 0 || rows < AT_BM;
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < AT_BN; ++c) {
+        for (int c = 0; c < HC; ++c) {
           const int key = key0 + c;
           if (key < lo || key > hi) s[c] = -INFINITY;
         }
@@ -312,31 +318,34 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // row maximum of the raw scores (the scale is positive), four chains
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < AT_BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
+      for (int c = 0; c < HC; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      xch[(b * 2 + grp) * AT_BM + r] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(mx, xch[(b * 2 + (grp ^ 1)) * AT_BM + r]) * a.scale_log2;
       const float m_new = fmaxf(m, mx);
       const float mbase = (m_new == -INFINITY) ? 0.f : m_new;
       const float corr = (m == -INFINITY) ? 0.f : fast_exp2(m - mbase);
       m = m_new;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[AT_BN / 2];
+      uint32_t pk[HC / 2];
 #pragma unroll
-      for (int c = 0; c < AT_BN; c += 2) {
+      for (int c = 0; c < HC; c += 2) {
         const float e0 = fast_exp2(fmaf(s[c], a.scale_log2, -mbase));
         const float e1 = fast_exp2(fmaf(s[c + 1], a.scale_log2, -mbase));
         sum4[(c >> 1) & 3] += e0 + e1;
         pk[c / 2] = pack2(e0, e1);
       }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      l = l * corr + sum;
+      l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));   // this group's share of l
 
       // P_j into shared memory, K-major [128 rows][64 keys] under the 128-byte swizzle
       if (!wait_warp(&p_empty[b], (((uint32_t)(j >> 1)) & 1) ^ 1)) { ok = false; break; }
       {
         uint8_t* prow = p_s + b * Cfg::P_BYTES + r * 128;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const uint4 w = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+        for (int c4 = 0; c4 < HC / 8; ++c4) {
+          const int ch = grp * (HC / 8) + c4;
+          const uint4 w = make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
           *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = w;
         }
       }
@@ -353,17 +362,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         atomicCAS(a.error, 0, GB_ERR_AT_TIMEOUT);
         *abort_flag = 1;
       }
-    } else if (r < rows) {
-      const float inv = 1.0f / l;
-      bf16* orow = a.out + ((size_t)(tok0 + r) * a.nq + h) * D;
+    } else {
+      // the two halves of l meet, then each group stores its half of the row
+      xch[(4 + grp) * AT_BM + r] = l;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const float inv = 1.0f / (l + xch[(4 + (grp ^ 1)) * AT_BM + r]);
+      if (r < rows) {
+        bf16* orow = a.out + ((size_t)(tok0 + r) * a.nq + h) * D + grp * HD;
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 8) {
-        uint4 w;
-        w.x = pack2(o[c0] * inv, o[c0 + 1] * inv);
-        w.y = pack2(o[c0 + 2] * inv, o[c0 + 3] * inv);
-        w.z = pack2(o[c0 + 4] * inv, o[c0 + 5] * inv);
-        w.w = pack2(o[c0 + 6] * inv, o[c0 + 7] * inv);
-        *reinterpret_cast<uint4*>(orow + c0) = w;
+        for (int c0 = 0; c0 < HD; c0 += 8) {
+          uint4 w;
+          w.x = pack2(o[c0] * inv, o[c0 + 1] * inv);
+          w.y = pack2(o[c0 + 2] * inv, o[c0 + 3] * inv);
+          w.z = pack2(o[c0 + 4] * inv, o[c0 + 5] * inv);
+          w.w = pack2(o[c0 + 6] * inv, o[c0 + 7] * inv);
+          *reinterpret_cast<uint4*>(orow + c0) = w;
+        }
       }
     }
   }
