@@ -30,6 +30,18 @@
 // for its copies in flight, frees its tensor memory and returns.
 #include "tc_common.cuh"
 
+#ifndef TC_SMALL_STAGES
+#define TC_SMALL_STAGES 8
+#endif
+#ifndef TC_SHARE_16
+#define TC_SHARE_16 6
+#endif
+#ifndef TC_SHARE_32
+#define TC_SHARE_32 4
+#endif
+#ifndef TC_SHARE_64
+#define TC_SHARE_64 4
+#endif
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
@@ -48,7 +60,13 @@ struct TcArgs {
   int transpose_out, out_f32;
   int silu;             // transposed output only: rows of A are gate|up interleaved in eights
   int dep_b;            // which operand an earlier kernel writes: 1 = B, 0 = A
+  unsigned long long* stamps;   // optional [blocks][8] %globaltimer stamps of the phases, or null
 };
+
+#define TC_STAMP(slot)                                                       \
+  do {                                                                       \
+    if (a.stamps) a.stamps[(size_t)blockIdx.x * 8 + (slot)] = now_ns();      \
+  } while (0)
 
 __device__ __forceinline__ int tc_block_of_unit(long long u, long long U, int P) {
   return (int)(((u + 1) * P - 1) / U);
@@ -59,7 +77,10 @@ struct TcConfig {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // both multiples of 1024
-  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);
+  // As deep a ring as shared memory allows.  (Halving it so that the next product's
+  // block fits beside this one and streams during its fixup tail was measured: the
+  // shallower ring cost more than the overlap gained.)
+  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : TC_SMALL_STAGES);
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256;
   // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
@@ -68,7 +89,7 @@ struct TcConfig {
 };
 
 template <int BN>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const TcArgs a) {
   using Cfg = TcConfig<BN>;
@@ -87,6 +108,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int P = gridDim.x, p = blockIdx.x;
+  if (threadIdx.x == 0) TC_STAMP(0);
   const int tiles_a = (a.rowsA + TC_BM - 1) / TC_BM, tiles_b = (a.rowsB + BN - 1) / BN;
   const int kblocks = (a.K + TC_BK - 1) / TC_BK;
   const long long U = (long long)tiles_a * tiles_b * kblocks;
@@ -115,6 +137,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
+  if (threadIdx.x == 0) TC_STAMP(1);
 
   // Only the producer lane waits for the kernel before this one (see below): the
   // MMAs need its loads and the epilogue needs the MMAs, so nothing here reads or
@@ -141,6 +164,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         issue(it, a.dep_b != 0, a.dep_b == 0);
       }
       pdl_wait();
+      TC_STAMP(2);
       for (long long it = 0; it < n_early; ++it) issue(it, a.dep_b == 0, a.dep_b != 0);
       bool ok = true;
       long long it = n_early;
@@ -157,6 +181,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         issue(it, true, true);
       }
       pdl_launch_dependents();
+      TC_STAMP(3);
       // Every load issued above completes on a `full` barrier that the MMA warp
       // waits for (or, after an abort, that is waited for below).
       if (!ok) {   // after an abort: let the copies in flight land before the block exits
@@ -192,6 +217,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             break;
           }
           tc_fence_after();
+          if (it == 0) TC_STAMP(4);
           const uint32_t sa = smem_u32(tiles_base + (size_t)s * Cfg::STAGE_BYTES);
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + Cfg::A_BYTES);
 #pragma unroll
@@ -201,6 +227,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if (ok) tc_commit(&acc_full[ab]);
       }
+      TC_STAMP(5);
     }
   } else {
     // ---------------------------------------------------------------- epilogue
@@ -320,7 +347,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               const int cb = tb * BN + c0 + j;
               if ((lane & 15) < 8 && row_a < a.rowsA && cb < a.rowsB) {
                 const size_t o = (size_t)cb * a.ld + (size_t)(row_a >> 4) * 8 + (row_a & 7);
-                const float val = f[j] / (1.0f + expf(-f[j])) * up;
+                // bf16 output: the fast exponential and reciprocal are far inside its rounding
+                const float val = f[j] * __frcp_rn(1.0f + __expf(-f[j])) * up;
                 if (a.out_f32) ((float*)a.out)[o] = val;
                 else ((bf16*)a.out)[o] = __float2bfloat16_rn(val);
               }
@@ -379,8 +407,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 
   // ---------------------------------------------------------------- teardown
+  if (threadIdx.x == 64) TC_STAMP(6);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TC_STAMP(7);
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
@@ -420,6 +450,12 @@ static int tc_plan(int rowsA, int rowsB, int K, TcPlan* pl) {
   const long long units = tiles * ((K + TC_BK - 1) / TC_BK);
   if (tiles > (1 << 30)) return GB_ERR_UNSUPPORTED;
   long long blocks = units < sms ? units : sms;
+  // The block that finishes a shared tile reads every contributor's partial
+  // (128 x BN floats each), one after the other.  With many activation rows that
+  // tail outweighs what more blocks gain in streaming, so the number of blocks
+  // that may share a tile is capped.
+  const long long share = bn <= 16 ? TC_SHARE_16 : (bn <= 32 ? TC_SHARE_32 : TC_SHARE_64);
+  if (blocks > tiles * share) blocks = tiles * share;
   pl->bn = bn;
   pl->blocks = (int)blocks;
   pl->scratch_floats = (int)(2 * blocks * bn * TC_BM);

@@ -383,7 +383,7 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
 class _TcArgs(ctypes.Structure):
     _fields_ = [("out", _P), ("scratch", _P), ("counters", _P), ("error", _P), ("rowsA", _I),
                 ("rowsB", _I), ("K", _I), ("ld", _I), ("transpose_out", _I), ("out_f32", _I),
-                ("silu", _I), ("dep_b", _I)]
+                ("silu", _I), ("dep_b", _I), ("stamps", _P)]
 
 
 _TC_PLANS = {}
@@ -413,7 +413,8 @@ def check_kernel_errors() -> None:
 
 
 def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
-                 swap: Optional[bool] = None, silu_mul: bool = False) -> torch.Tensor:
+                 swap: Optional[bool] = None, silu_mul: bool = False,
+                 stamps: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in
     tensor memory).  ``swap``: put the weight rows on the 128-row side of the MMA
     and the activation rows on the narrow side (the layout for few rows); by
@@ -454,6 +455,7 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
         a.rowsA, a.rowsB, a.K, a.ld = A.shape[0], B.shape[0], K, n_out
         a.transpose_out, a.out_f32 = int(swap), int(out_dtype == torch.float32)
         a.silu, a.dep_b = int(silu_mul), int(swap)      # the activations are another kernel's output
+        a.stamps = _ptr(stamps)     # int64 [blocks, 8]: phase times of every block, for tuning
         _check(_fn("gemm_tc", "gb_gemm_tc_bf16", "pppp")(
             A.data_ptr(), B.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc_bf16")
     return y
