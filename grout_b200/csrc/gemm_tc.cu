@@ -61,7 +61,15 @@ struct TcArgs {
   int silu;             // transposed output only: rows of A are gate|up interleaved in eights
   int dep_b;            // which operand an earlier kernel writes: 1 = B, 0 = A
   unsigned long long* stamps;   // optional [blocks][8] %globaltimer stamps of the phases, or null
+  int split_k;          // > 0: plain split-K, see below
 };
+
+// split_k = S > 0 (transposed 32-bit output only): the grid is tiles x S blocks,
+// block (tile, s) multiplies the s-th share of K and stores its 32-bit partial at
+// out + s * rowsB * ld; nothing is reduced here.  The kernel that consumes the
+// product (the residual add of the next norm, the q/k preparation) adds the S
+// partials in order.  This takes the whole fixup (partial store, fence, counter,
+// reload) off the end of the small projections of a decode step.
 
 #define TC_STAMP(slot)                                                       \
   do {                                                                       \
@@ -112,7 +120,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int tiles_a = (a.rowsA + TC_BM - 1) / TC_BM, tiles_b = (a.rowsB + BN - 1) / BN;
   const int kblocks = (a.K + TC_BK - 1) / TC_BK;
   const long long U = (long long)tiles_a * tiles_b * kblocks;
-  const long long u_begin = p * U / P, u_end = (p + 1) * U / P;
+  long long u_begin = p * U / P, u_end = (p + 1) * U / P;
+  int split_index = 0;
+  if (a.split_k > 0) {   // block p = tile * S + s takes the s-th share of its tile's k-blocks
+    const int tile = p / a.split_k;
+    split_index = p - tile * a.split_k;
+    u_begin = (long long)tile * kblocks + (long long)split_index * kblocks / a.split_k;
+    u_end = (long long)tile * kblocks + (long long)(split_index + 1) * kblocks / a.split_k;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -259,7 +274,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(ab * BN);
-      const bool whole = kb_lo == 0 && kb_hi == kblocks;
+      const bool whole = a.split_k > 0 || (kb_lo == 0 && kb_hi == kblocks);
       const int row_a = ta * TC_BM + r;
       bool write_out = whole;
       int p_first = 0, p_last = 0;
@@ -361,7 +376,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int cb = tb * BN + c0 + j;
                 if (cb < a.rowsB) {
                   const size_t o = (size_t)cb * a.ld + row_a;
-                  if (a.out_f32) ((float*)a.out)[o] = f[j];
+                  if (a.out_f32) ((float*)a.out)[o + (size_t)split_index * a.rowsB * a.ld] = f[j];
                   else ((bf16*)a.out)[o] = __float2bfloat16_rn(f[j]);
                 }
               }
@@ -437,6 +452,18 @@ struct TcPlan {
   int bn, blocks, scratch_floats, counters;
 };
 
+// How many ways K is cut when the consumer adds the partials (split_k mode): as
+// many blocks as fill the GPU once, at least four k-blocks each, at most 8 ways.
+static int tc_split(int rowsA, int rowsB, int K, int sms) {
+  const int bn = rowsB <= 16 ? 16 : (rowsB <= 32 ? 32 : (rowsB <= 64 ? 64 : (rowsB <= 128 ? 128 : 256)));
+  const long long tiles = (long long)((rowsA + TC_BM - 1) / TC_BM) * ((rowsB + bn - 1) / bn);
+  const int kblocks = (K + TC_BK - 1) / TC_BK;
+  long long s = sms / tiles;
+  if (s > kblocks / 4) s = kblocks / 4;
+  if (s > 8) s = 8;
+  return s < 2 ? 0 : (int)s;   // 0: not worth it (the product already has enough tiles)
+}
+
 static int tc_plan(int rowsA, int rowsB, int K, TcPlan* pl) {
   static int sms = 0;
   if (!sms) {
@@ -482,17 +509,23 @@ static int check_shape(int rowsA, int rowsB, int K) {
   return 0;
 }
 
-// plan[0] = BN, plan[1] = blocks, plan[2] = scratch floats, plan[3] = counters.
+// plan[0] = BN, plan[1] = blocks, plan[2] = scratch floats, plan[3] = counters,
+// plan[4] = the split count a split_k launch of this shape would use (0: none).
 GB_EXPORT int gb_gemm_tc_plan(int rowsA, int rowsB, int K, int* plan) {
   int e = check_shape(rowsA, rowsB, K);
   if (e) return e;
   TcPlan pl;
   e = tc_plan(rowsA, rowsB, K, &pl);
   if (e) return e;
+  int sms = 0, dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return GB_ERR_UNSUPPORTED;
   plan[0] = pl.bn;
   plan[1] = pl.blocks;
   plan[2] = pl.scratch_floats;
   plan[3] = pl.counters;
+  plan[4] = tc_split(rowsA, rowsB, K, sms);
   return 0;
 }
 
@@ -506,6 +539,12 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   TcPlan pl;
   e = tc_plan(args->rowsA, args->rowsB, args->K, &pl);
   if (e) return e;
+  if (args->split_k > 0) {
+    if (!args->transpose_out || !args->out_f32 || args->silu) return GB_ERR_UNSUPPORTED;
+    const int tiles = ((args->rowsA + TC_BM - 1) / TC_BM) * ((args->rowsB + pl.bn - 1) / pl.bn);
+    if (args->split_k > (args->K + TC_BK - 1) / TC_BK) return GB_ERR_BAD_ARG;
+    pl.blocks = tiles * args->split_k;
+  }
   CUtensorMap ma, mb;
   e = make_map(&ma, A, args->rowsA, args->K, TC_BM);
   if (e) return e;

@@ -12,8 +12,12 @@
 // the batch it is in.
 #include "common.cuh"
 
+// `parts`: instead of (or beside) delta, n_parts 32-bit partial sums [n_parts]
+// [rows_total, N], part_stride floats apart, added in order: the split-K product
+// of the projection before this norm leaves its reduction to this kernel.
 template <typename T, typename WT>
-__global__ void add_rmsnorm_kernel(const float* res_in, const T* delta,
+__global__ void add_rmsnorm_kernel(const float* res_in, const T* delta, const float* parts,
+                                   int n_parts, long long part_stride,
                                    const int* __restrict__ rows, const WT* __restrict__ w,
                                    float eps, float* res_out, T* __restrict__ y, int N) {
   __shared__ float scratch[32];
@@ -24,9 +28,15 @@ __global__ void add_rmsnorm_kernel(const float* res_in, const T* delta,
   const float* rin = res_in ? res_in + s * N : nullptr;
   const T* din = delta ? delta + s * N : nullptr;
   float* rout = res_out ? res_out + (size_t)r * N : nullptr;
+  const float* pin = parts ? parts + s * N : nullptr;
+  auto value = [&](int i) {
+    float d = din ? to_f32<T>(din[i]) : 0.f;
+    for (int k = 0; k < n_parts; ++k) d += pin[(size_t)k * part_stride + i];
+    return (rin ? rin[i] : 0.f) + d;
+  };
   float ss = 0.f;
   for (int i = threadIdx.x; i < N; i += blockDim.x) {
-    float v = (rin ? rin[i] : 0.f) + (din ? to_f32<T>(din[i]) : 0.f);
+    float v = value(i);
     if (rout) rout[i] = v;
     ss += v * v;
   }
@@ -36,7 +46,7 @@ __global__ void add_rmsnorm_kernel(const float* res_in, const T* delta,
   T* yo = y + (size_t)r * N;
   for (int i = threadIdx.x; i < N; i += blockDim.x) {
     // the same thread wrote rout[i] above, so it reads its own store here
-    float v = rout ? rout[i] : ((rin ? rin[i] : 0.f) + (din ? to_f32<T>(din[i]) : 0.f));
+    float v = rout ? rout[i] : value(i);
     yo[i] = from_f32<T>(v * inv * to_f32<WT>(w[i]));
   }
 }
@@ -72,7 +82,8 @@ template <> struct Vec4<bf16> {
 };
 
 template <typename T, typename WT>
-__global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta,
+__global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta, const float* parts,
+                                       int n_parts, long long part_stride,
                                        const int* __restrict__ rows, const WT* __restrict__ w,
                                        float eps, float* res_out, T* __restrict__ y, int N) {
   __shared__ float scratch[32];
@@ -90,6 +101,7 @@ __global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta,
   const float* rin = res_in ? res_in + s * N : nullptr;
   const T* din = delta ? delta + s * N : nullptr;
   float* rout = res_out ? res_out + (size_t)r * N : nullptr;
+  const float* pin = parts ? parts + s * N : nullptr;
   float v[NV_MAX][4];
   float ss = 0.f;
 #pragma unroll
@@ -99,6 +111,12 @@ __global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta,
       float a[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};
       if (rin) Vec4<float>::load(rin + i, a);
       if (din) Vec4<T>::load(din + i, d);
+      for (int k = 0; k < n_parts; ++k) {
+        float pk[4];
+        Vec4<float>::load(pin + (size_t)k * part_stride + i, pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) d[e] += pk[e];
+      }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         v[j][e] = a[e] + d[e];
@@ -132,36 +150,47 @@ static int norm_threads(int N) {
 }
 
 template <typename T, typename WT>
-static int launch(const float* res_in, const void* delta, const int* rows, const void* w, float eps,
+static int launch(const float* res_in, const void* delta, const float* parts, int n_parts,
+                  long long part_stride, const int* rows, const void* w, float eps,
                   float* res_out, void* y, int n_rows, int N, cudaStream_t stream) {
-  if (n_rows < 0 || N <= 0 || !w || !y || (!res_in && !delta)) return GB_ERR_BAD_ARG;
+  if (n_rows < 0 || N <= 0 || !w || !y || (!res_in && !delta && !parts)) return GB_ERR_BAD_ARG;
+  if ((parts != nullptr) != (n_parts > 0) || n_parts < 0) return GB_ERR_BAD_ARG;
   // in place is allowed only without a row list (each block then owns its row)
   if (rows && res_out && res_out == res_in) return GB_ERR_BAD_ARG;
   if (n_rows == 0) return 0;
   const bool aligned = ((((uintptr_t)res_in) | ((uintptr_t)delta) | ((uintptr_t)w) |
-                         ((uintptr_t)res_out) | ((uintptr_t)y)) & 15) == 0;
+                         ((uintptr_t)res_out) | ((uintptr_t)y) | ((uintptr_t)parts) |
+                         ((uintptr_t)(part_stride * 4))) & 15) == 0;
   if (N % 4 == 0 && N <= 4 * 1024 * NV_MAX && aligned) {
     int threads = (N / 4 + NV_MAX - 1) / NV_MAX;      // vectors per thread <= NV_MAX
     threads = ((threads + 31) / 32) * 32;
     if (threads < 64) threads = 64;
     if (threads > 1024) threads = 1024;
     return gb_launch(add_rmsnorm_vec_kernel<T, WT>, dim3(n_rows), dim3(threads), 0, stream, res_in,
-                     (const T*)delta, rows, (const WT*)w, eps, res_out, (T*)y, N);
+                     (const T*)delta, parts, n_parts, part_stride, rows, (const WT*)w, eps, res_out,
+                     (T*)y, N);
   }
   return gb_launch(add_rmsnorm_kernel<T, WT>, dim3(n_rows), dim3(norm_threads(N)), 0, stream, res_in,
-                   (const T*)delta, rows, (const WT*)w, eps, res_out, (T*)y, N);
+                   (const T*)delta, parts, n_parts, part_stride, rows, (const WT*)w, eps, res_out,
+                   (T*)y, N);
 }
 
 // w_is_f32: the weight vector is stored in 32-bit although the activations are bf16.
-GB_EXPORT int gb_add_rmsnorm_f32(const float* res_in, const void* delta, const int* rows,
+GB_EXPORT int gb_add_rmsnorm_f32(const float* res_in, const void* delta, const float* parts,
+                                 int n_parts, long long part_stride, const int* rows,
                                  const void* w, int w_is_f32, float eps, float* res_out, void* y,
                                  int n_rows, int N, cudaStream_t s) {
   if (!w_is_f32) return GB_ERR_UNSUPPORTED;
-  return launch<float, float>(res_in, delta, rows, w, eps, res_out, y, n_rows, N, s);
+  return launch<float, float>(res_in, delta, parts, n_parts, part_stride, rows, w, eps, res_out, y,
+                              n_rows, N, s);
 }
-GB_EXPORT int gb_add_rmsnorm_bf16(const float* res_in, const void* delta, const int* rows,
+GB_EXPORT int gb_add_rmsnorm_bf16(const float* res_in, const void* delta, const float* parts,
+                                  int n_parts, long long part_stride, const int* rows,
                                   const void* w, int w_is_f32, float eps, float* res_out, void* y,
                                   int n_rows, int N, cudaStream_t s) {
-  if (w_is_f32) return launch<bf16, float>(res_in, delta, rows, w, eps, res_out, y, n_rows, N, s);
-  return launch<bf16, bf16>(res_in, delta, rows, w, eps, res_out, y, n_rows, N, s);
+  if (w_is_f32)
+    return launch<bf16, float>(res_in, delta, parts, n_parts, part_stride, rows, w, eps, res_out, y,
+                               n_rows, N, s);
+  return launch<bf16, bf16>(res_in, delta, parts, n_parts, part_stride, rows, w, eps, res_out, y,
+                            n_rows, N, s);
 }

@@ -23,6 +23,9 @@ struct QkPrepareArgs {
   void* v_pages;
   float eps;
   int n_tokens, nq, nkv, D, rot_dim, max_pages, page;
+  const float* qkv_parts;   // instead of qkv: n_parts 32-bit partial sums of it, added in order
+  int n_parts;              //   (the split-K projection leaves its reduction to this kernel)
+  long long part_stride;    //   floats between partials
 };
 
 template <typename T, typename WT>
@@ -39,7 +42,16 @@ __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
   float* x = sm + warp * D;
   const T* src = (const T*)a.qkv + ((size_t)t * n_heads + head) * D;
   const int kind = head < a.nq ? 0 : (head < a.nq + a.nkv ? 1 : 2);
-  for (int d = lane; d < D; d += 32) x[d] = to_f32<T>(src[d]);
+  if (a.qkv_parts) {
+    const float* ps = a.qkv_parts + ((size_t)t * n_heads + head) * D;
+    for (int d = lane; d < D; d += 32) {
+      float v = 0.f;
+      for (int k = 0; k < a.n_parts; ++k) v += ps[(size_t)k * a.part_stride + d];
+      x[d] = v;
+    }
+  } else {
+    for (int d = lane; d < D; d += 32) x[d] = to_f32<T>(src[d]);
+  }
   __syncwarp();
   pdl_launch_dependents_if_large();
   const WT* w = kind == 0 ? (const WT*)a.q_w : (kind == 1 ? (const WT*)a.k_w : nullptr);
@@ -107,7 +119,17 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
 #pragma unroll
   for (int p = 0; p < NP; ++p) {
     const int j = 2 * lane + 64 * p;
-    if (j < HALF) {
+    if (j < HALF && a.qkv_parts) {
+      const float* ps = a.qkv_parts + ((size_t)t * n_heads + head) * D;
+      float2 l2 = make_float2(0.f, 0.f), h2 = make_float2(0.f, 0.f);
+      for (int k = 0; k < a.n_parts; ++k) {
+        const float2 lk = *reinterpret_cast<const float2*>(ps + (size_t)k * a.part_stride + j);
+        const float2 hk = *reinterpret_cast<const float2*>(ps + (size_t)k * a.part_stride + HALF + j);
+        l2.x += lk.x; l2.y += lk.y; h2.x += hk.x; h2.y += hk.y;
+      }
+      lo[p][0] = l2.x; lo[p][1] = l2.y;
+      hi[p][0] = h2.x; hi[p][1] = h2.y;
+    } else if (j < HALF) {
       const __nv_bfloat162 l2 = *reinterpret_cast<const __nv_bfloat162*>(src + j);
       const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(src + HALF + j);
       lo[p][0] = __low2float(l2); lo[p][1] = __high2float(l2);
@@ -216,7 +238,10 @@ static int launch(const QkPrepareArgs& a, cudaStream_t stream) {
 }
 
 static int check(const QkPrepareArgs& a) {
-  if (a.n_tokens < 0 || a.nq <= 0 || a.nkv < 0 || a.D <= 0 || !a.qkv || !a.q_out) return GB_ERR_BAD_ARG;
+  if (a.n_tokens < 0 || a.nq <= 0 || a.nkv < 0 || a.D <= 0 || (!a.qkv && !a.qkv_parts) || !a.q_out)
+    return GB_ERR_BAD_ARG;
+  if (a.qkv_parts && (a.n_parts <= 0 || (a.part_stride & 1) || (((uintptr_t)a.qkv_parts) & 7)))
+    return GB_ERR_BAD_ARG;
   if (a.inv_freq && (a.rot_dim <= 0 || a.rot_dim > a.D || (a.rot_dim & 1))) return GB_ERR_BAD_ARG;
   if (a.k_pages && (!a.v_pages || !a.block_table || !a.slots || !a.token_seq || a.page <= 0 ||
                     a.max_pages <= 0))

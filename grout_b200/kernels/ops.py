@@ -112,8 +112,15 @@ def add_rmsnorm(res_in: Optional[torch.Tensor], delta: Optional[torch.Tensor],
                 rows: Optional[torch.Tensor] = None, write_res: bool = True
                 ) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
     """(res_in + delta) in 32-bit -> (residual, normed).  Without ``rows`` the
-    residual is updated in place when ``res_in`` is given."""
-    src = res_in if res_in is not None else delta
+    residual is updated in place when ``res_in`` is given.  ``delta`` may also be
+    a stack of 32-bit partial sums [S, T, N] (what a split-K product leaves): they
+    are added in order."""
+    parts = None
+    if delta is not None and delta.dim() == 3:
+        _need(delta, "partial sums", torch.float32, 3)
+        parts, delta = delta, None
+    src = res_in if res_in is not None else (delta if delta is not None else
+                                             (parts[0] if parts is not None else None))
     if src is None:
         raise KernelError("add_rmsnorm needs a residual or a delta")
     if res_in is not None:
@@ -122,6 +129,8 @@ def add_rmsnorm(res_in: Optional[torch.Tensor], delta: Optional[torch.Tensor],
         _need(delta, "delta", dtype, 2)
         if res_in is not None and delta.shape != res_in.shape:
             raise KernelError(f"residual {tuple(res_in.shape)} and delta {tuple(delta.shape)} differ")
+    if parts is not None and res_in is not None and tuple(parts.shape[1:]) != tuple(res_in.shape):
+        raise KernelError(f"residual {tuple(res_in.shape)} and partial sums {tuple(parts.shape)} differ")
     _need(weight, "norm weight", ndim=1)
     N = src.shape[1]
     if weight.shape[0] != N:
@@ -142,9 +151,10 @@ def add_rmsnorm(res_in: Optional[torch.Tensor], delta: Optional[torch.Tensor],
             res_out = torch.empty((n_rows, N), dtype=torch.float32, device=src.device)
     y = torch.empty((n_rows, N), dtype=dtype, device=src.device)
     sfx = _suffix(dtype)
-    _check(_fn("norm", f"gb_add_rmsnorm_{sfx}", "ppppifppiip")(
-        _ptr(res_in), _ptr(delta), _ptr(rows), weight.data_ptr(), int(w_is_f32), float(eps),
-        _ptr(res_out), y.data_ptr(), n_rows, N, _stream()), "add_rmsnorm")
+    _check(_fn("norm", f"gb_add_rmsnorm_{sfx}", "pppilppifppiip")(
+        _ptr(res_in), _ptr(delta), _ptr(parts), 0 if parts is None else parts.shape[0],
+        0 if parts is None else parts.stride(0), _ptr(rows), weight.data_ptr(), int(w_is_f32),
+        float(eps), _ptr(res_out), y.data_ptr(), n_rows, N, _stream()), "add_rmsnorm")
     return res_out, y
 
 
@@ -154,20 +164,30 @@ class _QkPrepareArgs(ctypes.Structure):
                 ("token_pos", _P), ("slots", _P), ("block_table", _P), ("q_out", _P),
                 ("kv_out", _P), ("k_pages", _P), ("v_pages", _P), ("eps", _F),
                 ("n_tokens", _I), ("nq", _I), ("nkv", _I), ("D", _I), ("rot_dim", _I),
-                ("max_pages", _I), ("page", _I)]
+                ("max_pages", _I), ("page", _I), ("qkv_parts", _P), ("n_parts", _I),
+                ("part_stride", _L)]
 
 
 def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=None,
                eps: float = 0.0, inv_freq=None, rot_dim: int = 0, token_seq, token_pos, slots,
                block_table=None, k_pages=None, v_pages=None, page: int = 0,
                want_kv_out: bool = False):
-    """Returns (q [T, nq, D], kv_out or None); writes k, v into the pages when given."""
-    _need(qkv, "qkv", ndim=2)
-    T = qkv.shape[0]
-    if qkv.shape[1] != (nq + 2 * nkv) * D:
-        raise KernelError(f"qkv has {qkv.shape[1]} columns, expected (nq + 2 nkv) * D = "
+    """Returns (q [T, nq, D], kv_out or None); writes k, v into the pages when given.
+    ``qkv`` may be a stack of 32-bit partial sums [S, T, width] of the projection
+    (bf16 engines only): they are added in order."""
+    parts = None
+    if qkv.dim() == 3:
+        _need(qkv, "qkv partial sums", torch.float32, 3)
+        if k_pages is not None and k_pages.dtype != torch.bfloat16:
+            raise KernelError("partial sums of qkv are taken with a bfloat16 cache only")
+        parts, dt = qkv, torch.bfloat16
+    else:
+        _need(qkv, "qkv", ndim=2)
+        dt = qkv.dtype
+    T = qkv.shape[-2]
+    if qkv.shape[-1] != (nq + 2 * nkv) * D:
+        raise KernelError(f"qkv has {qkv.shape[-1]} columns, expected (nq + 2 nkv) * D = "
                           f"{(nq + 2 * nkv) * D}")
-    dt = qkv.dtype
     w_is_f32 = 0
     for w, nm in ((q_w, "q norm weight"), (k_w, "k norm weight")):
         if w is not None:
@@ -187,7 +207,10 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
     q = torch.empty((T, nq, D), dtype=dt, device=qkv.device)
     kv_out = torch.empty((T, 2 * nkv, D), dtype=dt, device=qkv.device) if want_kv_out else None
     a = _QkPrepareArgs()
-    a.qkv, a.q_w, a.k_w, a.inv_freq = qkv.data_ptr(), _ptr(q_w), _ptr(k_w), _ptr(inv_freq)
+    a.qkv, a.q_w, a.k_w, a.inv_freq = (None if parts is not None else qkv.data_ptr()), _ptr(q_w), \
+        _ptr(k_w), _ptr(inv_freq)
+    if parts is not None:
+        a.qkv_parts, a.n_parts, a.part_stride = parts.data_ptr(), parts.shape[0], parts.stride(0)
     a.token_seq, a.token_pos, a.slots = token_seq.data_ptr(), token_pos.data_ptr(), slots.data_ptr()
     a.q_out, a.kv_out = q.data_ptr(), _ptr(kv_out)
     a.eps, a.n_tokens, a.nq, a.nkv, a.D, a.rot_dim = float(eps), T, nq, nkv, D, int(rot_dim)
@@ -383,7 +406,7 @@ def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
 class _TcArgs(ctypes.Structure):
     _fields_ = [("out", _P), ("scratch", _P), ("counters", _P), ("error", _P), ("rowsA", _I),
                 ("rowsB", _I), ("K", _I), ("ld", _I), ("transpose_out", _I), ("out_f32", _I),
-                ("silu", _I), ("dep_b", _I), ("stamps", _P)]
+                ("silu", _I), ("dep_b", _I), ("stamps", _P), ("split_k", _I)]
 
 
 _TC_PLANS = {}
@@ -414,13 +437,17 @@ def check_kernel_errors() -> None:
 
 def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                  swap: Optional[bool] = None, silu_mul: bool = False,
-                 stamps: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 stamps: Optional[torch.Tensor] = None, split_out: bool = False) -> torch.Tensor:
     """x [M, K] . w [N, K]^T on the tcgen05 tensor cores (TMA-fed, accumulator in
     tensor memory).  ``swap``: put the weight rows on the 128-row side of the MMA
     and the activation rows on the narrow side (the layout for few rows); by
     default chosen when M <= 64.  ``silu_mul`` (with swap): the rows of ``w`` are
     gate and up rows interleaved in groups of 8 and the result is
-    silu(gate) * up, [M, N / 2]."""
+    silu(gate) * up, [M, N / 2].  ``split_out`` (with swap): when the product has
+    too few tiles to fill the GPU, K is cut S ways and the S 32-bit partial
+    products are returned as [S, M, N] for the consumer to add (its norm or q/k
+    preparation does so in the kernel it runs anyway); otherwise the result is the
+    ordinary [M, N]."""
     _need(x, "activations", torch.bfloat16, 2)
     _need(w, "weight", torch.bfloat16, 2)
     M, K = x.shape
@@ -443,17 +470,21 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
         key = (A.shape[0], B.shape[0], K, torch.cuda.current_device())
         plan = _TC_PLANS.get(key)
         if plan is None:
-            out = (c_int * 4)()
+            out = (c_int * 5)()
             _check(_fn("gemm_tc", "gb_gemm_tc_plan", "iiip")(
                 A.shape[0], B.shape[0], K, ctypes.addressof(out)), "gemm_tc_plan", 0)
-            plan = _TC_PLANS[key] = (out[0], out[1], out[2], out[3])
+            plan = _TC_PLANS[key] = (out[0], out[1], out[2], out[3], out[4])
+        split = plan[4] if (split_out and swap and not silu_mul) else 0
+        if split:
+            y = torch.empty((split, M, N), dtype=torch.float32, device=x.device)
         ws = _WORKSPACES.setdefault(x.device.index or 0, _Workspace())
         scratch, counters = ws.get(x.device, plan[2], plan[3])
         a = _TcArgs()
         a.out, a.scratch, a.counters = y.data_ptr(), scratch.data_ptr(), counters.data_ptr()
         a.error = _tc_error_flag(x.device).data_ptr()
         a.rowsA, a.rowsB, a.K, a.ld = A.shape[0], B.shape[0], K, n_out
-        a.transpose_out, a.out_f32 = int(swap), int(out_dtype == torch.float32)
+        a.transpose_out, a.out_f32 = int(swap), int(out_dtype == torch.float32 or bool(split))
+        a.split_k = split
         a.silu, a.dep_b = int(silu_mul), int(swap)      # the activations are another kernel's output
         a.stamps = _ptr(stamps)     # int64 [blocks, 8]: phase times of every block, for tuning
         _check(_fn("gemm_tc", "gb_gemm_tc_bf16", "pppp")(

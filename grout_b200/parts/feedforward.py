@@ -1,5 +1,6 @@
 """Feed-forward parts.  Interface of the family: ``forward(x, step) -> y`` with
-``x`` and ``y`` [T, hidden] in the compute dtype.  A feed-forward with experts
+``x`` and ``y`` [T, hidden] in the compute dtype (``y`` may be a stack of 32-bit
+partial sums [S, T, hidden], which the next norm adds: see ``Norm.add_norm``).  A feed-forward with experts
 routes inside ``forward``; the rows' packing is the step's and does not change.
 """
 from __future__ import annotations
@@ -55,4 +56,4 @@ class SwiGLU(FeedForward):
         return ("elementwise",) + self.gate_up.kernel_modules() + self.down.kernel_modules()
 
     def forward(self, x, step):
-        return self.down(self.gate_up.silu_mul(x, self.interleave))
+        return self.down(self.gate_up.silu_mul(x, self.interleave), partial_ok=True)

@@ -39,7 +39,12 @@ class Linear:
             return ("gemm_f32", "elementwise")
         return ("gemm_tc", "gemm_skinny_bf16")
 
-    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                 partial_ok: bool = False) -> torch.Tensor:
+        """``partial_ok``: the caller hands the result to a kernel that can add
+        32-bit partial sums (a norm's residual add, the q/k preparation); a product
+        with few rows and few tiles may then come back as [S, M, N] float32, its
+        split-K reduction left to that kernel."""
         out_dtype = out_dtype or x.dtype
         w = self.weight
         if w.dtype == torch.float32:
@@ -51,7 +56,7 @@ class Linear:
         if self.in_features % 8 == 0:
             if M <= ops.SKINNY_MAX_ROWS:
                 if self.decode_kernel == "tc":
-                    return ops.gemm_tc_bf16(x, w, out_dtype, swap=True)
+                    return ops.gemm_tc_bf16(x, w, out_dtype, swap=True, split_out=partial_ok)
                 return ops.gemm_skinny_bf16(x, w, out_dtype)
             if self.prefill_kernel == "tc":
                 return ops.gemm_tc_bf16(x, w, out_dtype, swap=False)

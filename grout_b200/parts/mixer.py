@@ -4,7 +4,8 @@ Interface of the family:
 
 * ``cache_spec()`` — ``KVSpec``, ``StateSpec`` or None: what one layer of this
   mixer keeps per sequence.  The cache groups layers with equal needs.
-* ``forward(x, step, cache) -> y`` — ``x`` [T, hidden] in the compute dtype,
+* ``forward(x, step, cache) -> y`` — ``x`` [T, hidden] in the compute dtype
+  (``y`` may be a stack of 32-bit partial sums [S, T, hidden]: see ``Norm.add_norm``),
   ``step`` the ``StepContext`` (which sequence and position each row has),
   ``cache`` the layer's view of its store (``KVLayerView`` / ``StateLayerView``).
   It must store what later steps need (keys, values, state) for the rows of
@@ -109,11 +110,13 @@ class GQAAttention(Mixer):
 
     def forward(self, x, step, cache):
         T = x.shape[0]
-        qkv = self.qkv(x)
         rot = self.position.rotary()
         if cache is None or (cache.spec.n_kv_heads, cache.spec.head_dim) != (self.nkv, self.D):
             raise ValueError(f"attention with {self.nkv} kv heads of {self.D} was given the cache "
                              f"{None if cache is None else cache.spec}")
+        fused = rot is not None or type(self.position).apply_qk is PositionEncoding.apply_qk
+        # the q/k preparation can add the partial sums of a split-K projection itself
+        qkv = self.qkv(x, partial_ok=fused and x.dtype == torch.bfloat16 and not self.shares_kv)
         if self.shares_kv:
             q, _ = ops.qk_prepare(qkv, self.nq, 0, self.D, q_w=self.q_norm_w,
                                   eps=self.qk_norm_eps or 0.0,
@@ -124,8 +127,7 @@ class GQAAttention(Mixer):
                 q, _k = self.position.apply_qk(q, q[:, :0], step.token_pos)
             attn = ops.attention(q.contiguous(), cache.k_pages, cache.v_pages, cache.block_table,
                                  step=step, page=cache.page, scale=self.scale, window=self.window)
-            return self.o(attn.view(T, self.nq * self.D))
-        fused = rot is not None or type(self.position).apply_qk is PositionEncoding.apply_qk
+            return self.o(attn.view(T, self.nq * self.D), partial_ok=True)
         common = dict(q_w=self.q_norm_w, k_w=self.k_norm_w, eps=self.qk_norm_eps or 0.0,
                       token_seq=step.token_seq, token_pos=step.token_pos, slots=step.slots)
         if fused:
@@ -147,4 +149,4 @@ class GQAAttention(Mixer):
             q = q.contiguous()
         attn = ops.attention(q, cache.k_pages, cache.v_pages, cache.block_table, step=step,
                              page=cache.page, scale=self.scale, window=self.window)
-        return self.o(attn.view(T, self.nq * self.D))
+        return self.o(attn.view(T, self.nq * self.D), partial_ok=True)

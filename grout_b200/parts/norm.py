@@ -4,8 +4,10 @@
 * ``add_norm(res, delta, rows=None) -> (res, y)``: adds ``delta`` (compute
   dtype, may be None) into the 32-bit residual stream ``res`` (may be None on
   the first layer), optionally keeps only ``rows``, and returns the updated
-  stream with its normalised rows.  The default does the two steps one after
-  the other; RMSNorm does both in one kernel.
+  stream with its normalised rows.  ``delta`` may also arrive as a stack of
+  32-bit partial sums [S, T, N] (a split-K projection leaves its reduction to
+  the norm); they are added in order.  The default does the steps one after the
+  other; RMSNorm does all of it in one kernel.
 """
 from __future__ import annotations
 
@@ -32,6 +34,8 @@ class Norm(Part):
 def residual_add(res, delta, rows=None) -> torch.Tensor:
     """32-bit residual sum for norms without a fused kernel (a library call on
     small tensors; parts of this package use the fused kernel instead)."""
+    if delta is not None and delta.dim() == 3:      # partial sums of a split-K product
+        delta = delta.sum(dim=0)
     if res is None:
         out = delta.float()
     elif delta is None:

@@ -70,3 +70,20 @@ def test_silu_epilogue(M, I, K):
     want = g / (1 + torch.exp(-g)) * u
     assert got.shape == (M, I)
     assert torch.allclose(got.double(), want, atol=2e-4, rtol=3 * 2.0 ** -8)
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 2560, 4096), (1, 6144, 2560), (64, 2560, 9728), (16, 128, 512)])
+def test_split_out_partials_sum_to_the_product(M, N, K):
+    """With few tiles the product may leave its split-K reduction to its consumer."""
+    from grout_b200.kernels import ops
+    x, w = _rand((M, K), 80), _rand((N, K), 81, 0.05)
+    got = ops.gemm_tc_bf16(x.to(DEV), w.to(DEV), torch.bfloat16, swap=True, split_out=True)
+    ops.check_kernel_errors()
+    assert got.dtype == torch.float32 and got.dim() == 3 and got.shape[1:] == (M, N)
+    assert got.shape[0] >= 2
+    want = x.double() @ w.double().T
+    assert torch.allclose(got.double().sum(0).cpu(), want, atol=2e-5 * math.sqrt(K), rtol=1e-5)
+    # a product with many tiles keeps its own reduction
+    big = ops.gemm_tc_bf16(x.to(DEV)[:, :256].contiguous(), _rand((19456, 256), 82, 0.05).to(DEV),
+                           torch.bfloat16, swap=True, split_out=True)
+    assert big.dim() == 2

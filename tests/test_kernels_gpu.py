@@ -464,3 +464,56 @@ def test_attn_prefill_tc(nq, nkv, D, window):
         assert torch.allclose(got[cu[s] + i].double(), want, **FAST_TOL), (s, i)
     if window is None:
         assert torch.allclose(got[cu[4] + 299, 0].double(), pc.v[4][3, 0].double(), atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("N", [200, 2560])
+def test_add_rmsnorm_takes_partial_sums(N):
+    """The residual add accepts the 32-bit partial sums of a split-K product."""
+    dt = torch.bfloat16
+    rows, S = 9, 5
+    res = _rand((rows, N), torch.float32, 90)
+    parts = _rand((S, rows, N), torch.float32, 91)
+    w = (1 + 0.1 * _rand((N,), torch.float32, 92)).to(dt)
+    want_res = res.double() + parts.double().sum(0)
+    want_y = plain.rms_norm(want_res, w, 1e-5)
+    r = res.clone().to(DEV)
+    res_out, y = _ops().add_rmsnorm(r, parts.to(DEV), w.to(DEV), 1e-5, dtype=dt)
+    assert torch.allclose(res_out.cpu().double(), want_res, atol=2e-6, rtol=1e-6)
+    assert torch.allclose(y.cpu().double(), want_y, atol=4 * _eps(dt), rtol=2 * _eps(dt))
+    idx = torch.tensor([8, 0, 3], dtype=torch.int32)
+    res2, y2 = _ops().add_rmsnorm(res.to(DEV), parts.to(DEV), w.to(DEV), 1e-5, dtype=dt, rows=idx.to(DEV))
+    assert torch.allclose(res2.cpu().double(), want_res[idx.long()], atol=2e-6, rtol=1e-6)
+    assert torch.allclose(y2.cpu().double(), want_y[idx.long()], atol=4 * _eps(dt), rtol=2 * _eps(dt))
+
+
+@pytest.mark.parametrize("nq,nkv,D", [(6, 2, 48), (8, 1, 128), (3, 3, 64)])
+def test_qk_prepare_takes_partial_sums(nq, nkv, D):
+    dt = torch.bfloat16
+    pc = Paged([3, 70], nkv, D, dt, 93)
+    places = [(0, 2), (1, 63), (1, 64)]
+    T, S = len(places), 3
+    width = (nq + 2 * nkv) * D
+    parts = _rand((S, T, width), torch.float32, 94)
+    whole = parts.double().sum(0)
+    q_w = (1 + 0.1 * _rand((D,), torch.float32, 95)).to(dt)
+    k_w = (1 + 0.1 * _rand((D,), torch.float32, 96)).to(dt)
+    theta, eps = 50000.0, 1e-5
+    inv = torch.from_numpy(plain.rope_inv_freq(D, theta))
+    pos = [p for _, p in places]
+    x = whole.view(T, nq + 2 * nkv, D)
+    cos, sin = plain.rope_cos_sin(pos, D, theta)
+    want_q = plain.apply_rope(plain.rms_norm(x[:, :nq], q_w, eps), cos, sin)
+    want_k = plain.apply_rope(plain.rms_norm(x[:, nq:nq + nkv], k_w, eps), cos, sin)
+    kp, vp = pc.k_pages.to(DEV), pc.v_pages.to(DEV)
+    q, _ = _ops().qk_prepare(
+        parts.to(DEV), nq, nkv, D, q_w=q_w.to(DEV), k_w=k_w.to(DEV), eps=eps, inv_freq=inv.to(DEV),
+        rot_dim=D, token_seq=torch.tensor([s for s, _ in places], dtype=torch.int32, device=DEV),
+        token_pos=torch.tensor(pos, dtype=torch.int32, device=DEV),
+        slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
+        block_table=pc.table.to(DEV), k_pages=kp, v_pages=vp, page=64)
+    tol = dict(atol=6 * _eps(dt), rtol=4 * _eps(dt))
+    assert q.dtype == dt and torch.allclose(q.cpu().double(), want_q, **tol)
+    for r, (s, p) in enumerate(places):
+        pg = int(pc.table[pc.slot_of[s], p // 64])
+        assert torch.allclose(kp[pg, :, p % 64].cpu().double(), want_k[r], **tol)
+        assert torch.allclose(vp[pg, :, p % 64].cpu().double(), x[r, nq + nkv:], **tol)
