@@ -104,22 +104,40 @@ static inline bool gb_pdl_enabled() {
   return on == 1;
 }
 
+// cluster_x > 1 launches thread-block clusters of that many blocks along x.
 template <typename... KArgs, typename... Args>
-static inline int gb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                            cudaStream_t stream, Args... args) {
+static inline int gb_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, int cluster_x, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (gb_pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = gb_pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = n;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
   if (e != cudaSuccess) return (int)e;
   return (int)cudaGetLastError();
+}
+
+template <typename... KArgs, typename... Args>
+static inline int gb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            cudaStream_t stream, Args... args) {
+  return gb_launch_cluster(kernel, grid, block, smem, stream, 1, args...);
 }
 
 // Address of row `pos` of kv head `h` of a sequence in a paged cache laid out

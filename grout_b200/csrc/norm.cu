@@ -10,7 +10,11 @@
 // store a 16-bit residual; here the residual stream itself stays 32-bit.
 // The reduction tree depends on N only, so a row's result does not depend on
 // the batch it is in.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 // `parts`: instead of (or beside) delta, n_parts 32-bit partial sums [n_parts]
 // [rows_total, N], part_stride floats apart, added in order: the split-K product
@@ -141,6 +145,66 @@ __global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta, cons
   }
 }
 
+// A handful of rows (a decode step) would keep a handful of SMs busy.  Here a
+// cluster of NC_CLUSTER blocks shares a row: each block owns a quarter of the
+// columns, the sums of squares meet through distributed shared memory (added in
+// rank order, so the result is a fixed sum), and every block scales its columns.
+// The cluster barrier is the hardware's; no block spins on memory.
+#define NC_CLUSTER 4
+template <typename T, typename WT>
+__global__ void add_rmsnorm_cluster_kernel(const float* res_in, const T* delta, const float* parts, int n_parts,
+                           long long part_stride, const int* __restrict__ rows,
+                           const WT* __restrict__ w, float eps, float* res_out,
+                           T* __restrict__ y, int N) {
+  __shared__ float scratch[32];
+  __shared__ float ss_mine;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  pdl_launch_dependents_if_small();
+  const int cols = N / NC_CLUSTER;              // a multiple of 4
+  const int c0 = rank * cols;
+  const int i = c0 + threadIdx.x * 4;           // this thread's four columns
+  const bool active = threadIdx.x * 4 < cols;
+  float wv[4] = {0.f, 0.f, 0.f, 0.f};
+  if (active) Vec4<WT>::load(w + i, wv);        // no kernel's output: before the wait
+  pdl_wait();
+  const int r = blockIdx.x / NC_CLUSTER;
+  const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  float ss = 0.f;
+  if (active) {
+    float a[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};
+    if (res_in) Vec4<float>::load(res_in + s * N + i, a);
+    if (delta) Vec4<T>::load(delta + s * N + i, d);
+    for (int k = 0; k < n_parts; ++k) {
+      float pk[4];
+      Vec4<float>::load(parts + (size_t)k * part_stride + s * N + i, pk);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) d[e] += pk[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      v[e] = a[e] + d[e];
+      ss += v[e] * v[e];
+    }
+    if (res_out) Vec4<float>::store(res_out + (size_t)r * N + i, v);
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0) ss_mine = ss;
+  cluster.sync();
+  float total = 0.f;
+#pragma unroll
+  for (int k = 0; k < NC_CLUSTER; ++k) total += *cluster.map_shared_rank(&ss_mine, k);
+  cluster.sync();   // nobody leaves while its sum may still be read
+  const float inv = 1.0f / sqrtf(total / (float)N + eps);
+  if (active) {
+    float o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = v[e] * inv * wv[e];
+    Vec4<T>::store(y + (size_t)r * N + i, o);
+  }
+}
+
 static int norm_threads(int N) {
   int t = (N + 3) / 4;
   t = ((t + 31) / 32) * 32;
@@ -161,6 +225,12 @@ static int launch(const float* res_in, const void* delta, const float* parts, in
   const bool aligned = ((((uintptr_t)res_in) | ((uintptr_t)delta) | ((uintptr_t)w) |
                          ((uintptr_t)res_out) | ((uintptr_t)y) | ((uintptr_t)parts) |
                          ((uintptr_t)(part_stride * 4))) & 15) == 0;
+  if (aligned && n_rows <= 64 && N >= 1024 && N % (4 * NC_CLUSTER) == 0 && N / NC_CLUSTER <= 4096) {
+    int threads = ((N / NC_CLUSTER / 4 + 31) / 32) * 32;
+    return gb_launch_cluster(add_rmsnorm_cluster_kernel<T, WT>, dim3(n_rows * NC_CLUSTER),
+                             dim3(threads), 0, stream, NC_CLUSTER, res_in, (const T*)delta, parts,
+                             n_parts, part_stride, rows, (const WT*)w, eps, res_out, (T*)y, N);
+  }
   if (N % 4 == 0 && N <= 4 * 1024 * NV_MAX && aligned) {
     int threads = (N / 4 + NV_MAX - 1) / NV_MAX;      // vectors per thread <= NV_MAX
     threads = ((threads + 31) / 32) * 32;

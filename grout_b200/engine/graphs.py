@@ -36,32 +36,52 @@ class DecodeGraph:
         self.staging = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(4)]
         self.copied = [None] * len(self.staging)
         self.turn = 0
+        self.off = off
+        self.views = []
+        for st in self.staging:          # numpy views of every array of the layout
+            flat = st.numpy()
+            v = {name: flat[o:o + cnt] for name, (o, cnt) in off.items()}
+            v["token_seq"][:] = np.arange(n_seqs, dtype=np.int32)
+            v["cu_q"][:] = np.arange(n_seqs + 1, dtype=np.int32)
+            v["want_rows"][:] = np.arange(n_seqs, dtype=np.int32)
+            self.views.append(v)
         self.dev = torch.zeros(total, dtype=torch.int32, device=device)
         self.graph = None
         self.logits = None
         self.kernels_per_replay = 0
 
     def _fill(self, entries) -> dict:
-        """Packs the live sequences plus padding rows and copies them to the device.
-        Every row's logits are computed: the head reads its weights once anyway."""
+        """Writes the live sequences plus padding rows into a staging buffer and
+        copies it to the device.  Every row's logits are computed: the head reads
+        its weights once anyway.  Only what changes from step to step (tokens,
+        slots, positions, lengths) is rewritten; the rest of the layout is constant
+        for a bucket and was filled when the buffer was made."""
         n_real = len(entries)
-        buf, meta = pack_step(entries, [[0]] * n_real, self.n - n_real)
-        full_off, total = layout_sizes(self.n, self.n, self.n)
         k = self.turn
         self.turn = (k + 1) % len(self.staging)
         if self.copied[k] is not None:
             self.copied[k].synchronize()
-        out = self.staging[k].numpy()
-        out[:] = 0
-        # want_rows is the last array, so all others sit at the same offsets
-        o_want, _ = full_off["want_rows"]
-        out[:o_want] = buf[:o_want]
-        out[o_want:o_want + self.n] = np.arange(self.n, dtype=np.int32)
+        out = self.views[k]
+        n = self.n
+        slots = [e[0] for e in entries]
+        starts = [e[1] for e in entries]
+        out["tokens"][:n_real] = [e[2][0] for e in entries]
+        out["tokens"][n_real:] = 0
+        out["token_pos"][:n_real] = starts
+        out["token_pos"][n_real:] = 0
+        out["slots"][:n_real] = slots
+        out["slots"][n_real:] = -1
+        out["kv_len"][:n_real] = starts
+        out["kv_len"][:n_real] += 1
+        out["kv_len"][n_real:] = 1
         self.dev.copy_(self.staging[k], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.copied[k] = ev
-        return dict(meta, off=full_off, n_want=self.n)
+        return dict(n_tokens=n, n_seqs=n, n_want=n, off=self.off, q_lens=(1,) * n,
+                    starts=tuple(starts) + (0,) * (n - n_real),
+                    slot_list=tuple(slots) + (-1,) * (n - n_real), decode=True, max_q_len=1,
+                    max_kv_len=max(starts, default=0) + 1)
 
     def _capture(self) -> None:
         """Warm-up with padding rows only (which store nothing), then capture."""
