@@ -4,37 +4,55 @@
 // programs, src/kernels.rs:1146-1295, 1513-1862; its online-softmax recurrence
 // in the log2 domain is the one used here.)
 //
-// One block owns 128 consecutive query rows of one sequence and one query head.
-// Key tiles are whole pages (64 keys).  Per key tile j:
-//   S_j  = Q K_j^T          tcgen05.mma, M 128 x N 64 x K head_dim, Q and K_j
-//                           K-major tiles that TMA wrote (128-byte swizzle)
-//   P_j  = 2^(S_j c - m_j)  softmax threads (one per query row) read S_j from
-//                           TMEM, mask, keep the row maximum m and sum l, and
-//                           write P_j as bf16 into shared memory in the same
-//                           swizzled K-major layout
-//   R_j  = P_j V_j          tcgen05.mma, M 128 x N head_dim x K 64, V_j read as
-//                           an MN-major operand straight from the page layout
-//   O    = O 2^(m_{j-1}-m_j) + R_j   in registers, one row per thread
-// S and R are double-buffered in TMEM (2 x 64 + 2 x head_dim columns), the K/V
-// ring has three stages, so the tensor cores work on tile j + 1 while tile j is
-// in the softmax.
+// One block owns 256 consecutive query rows of one sequence and one query head,
+// as two query blocks A and B of 128 rows that share every key tile.  Key tiles
+// are whole pages (64 keys).  Per key tile j and query block g:
+//   S_gj = Q_g K_j^T        tcgen05.mma, M 128 x N 64 x K head_dim; Q_g lives in
+//                           tensor memory for the whole block (the softmax threads
+//                           put their own query row there once), K_j is a K-major
+//                           tile that TMA wrote (128-byte swizzle)
+//   P_gj = 2^(S_gj c - b)   softmax threads (one per query row) read S_gj from
+//                           TMEM, mask, and write P_gj as bf16 into shared memory
+//                           in the swizzled K-major layout
+//   O_g += P_gj V_j         tcgen05.mma accumulating in TMEM, M 128 x N head_dim
+//                           x K 64, V_j read as an MN-major operand straight from
+//                           the page layout
+// Why Q sits in tensor memory: with one SM per tile the tensor core fetches its
+// shared-memory operands at about 64 bytes a cycle (measured: the issue of the
+// products, not their arithmetic, set the tile time), and Q was two thirds of
+// the bytes of the first product.
+// The base b of a row is its running maximum, but it is only raised (and the
+// row of O_g in TMEM rescaled) when the maximum has grown by more than 2^8, so
+// that the read-modify-write of O is rare; probabilities then stay below 256,
+// and the final division by l removes the base.
+// The two query blocks are two independent chains (barrier, TMEM load, softmax,
+// fence, barrier) that overlap each other and the tensor cores; P is double-
+// buffered per block, the K/V ring has four stages.
+// TMEM columns: Q 2 x head_dim/2, S 2 x 64, O 2 x head_dim.
 //
-// Warps: 0 = TMA producer (one lane), 1 = TMEM allocation and MMA issue (one
-// lane), 2-9 = softmax / accumulation / store: two threads per query row, each
-// with half of a tile's keys and half of head_dim, so that every scheduler of the
-// SM holds two such warps.
+// Warps: 0 = TMA producer (one lane), 1 = TMEM allocation and MMA issue for
+// query block A, 10 = MMA issue for block B (the warp walks an event loop, an
+// elected lane issues), 2-5 = softmax of block A (thread = query row), 6-9 = of
+// block B.  One issuing warp per query block: a single one was the bottleneck
+// (its waits, polls and blocking issues in series took longer than a softmax
+// tile), and it kept both blocks in lockstep.
 //
 // Pages must hold finite values in rows beyond a sequence's length (the cache is
 // zero-filled when it is made): those keys are masked to probability 0, and
 // 0 x NaN would still be NaN in the second product.
 // All mbarrier waits are bounded (see tc_common.cuh); on expiry the block sets
 // args.error, stops, frees its tensor memory and returns.
+// With -DAT_STAMPS the heaviest block of head 0 writes clock stamps behind the
+// error word (from 64 ints in; the caller must give it 2.5 KB of room): eight
+// per tile for tiles 8-11 of one softmax warp of each query block, then up to 96
+// issue events (clock << 20 | tile << 8 | block << 4 | 1 for S, 2 for PV) of
+// each issuing warp.  A tuning aid; never defined in the product build.
 #include "tc_common.cuh"
 
 #define AT_BM 128
 #define AT_BN 64
-#define AT_THREADS 320
-#define AT_STAGES 3
+#define AT_THREADS 352
+#define AT_STAGES 4
 
 #define GB_ERR_AT_TIMEOUT 111
 
@@ -73,62 +91,66 @@ __device__ __forceinline__ float fast_exp2(float x) {   // 2^x, one MUFU operati
 template <int DS>   // head_dim = 64 * DS
 struct AtConfig {
   static constexpr int D = 64 * DS;
-  static constexpr int Q_BYTES = AT_BM * 128 * DS;          // DS sub-tiles of [128][64]
   static constexpr int SUB_BYTES = AT_BN * 128;             // one [64 keys][64] sub-tile
   static constexpr int KV_BYTES = 2 * DS * SUB_BYTES;       // K and V of one stage
-  static constexpr int P_BYTES = AT_BM * 128;               // [128][64 keys]
-  static constexpr int TMEM_S = 0;                          // two S buffers of 64 columns
-  static constexpr int TMEM_R = 2 * AT_BN;                  // two R buffers of D columns
-  static constexpr int TMEM_COLS = (2 * AT_BN + 2 * D) <= 256 ? 256 : 512;
-  static constexpr size_t SMEM = (size_t)Q_BYTES + AT_STAGES * KV_BYTES + 2 * P_BYTES + 1024 + 256;
-  // S = Q K^T: both K-major, N = 64.   R = P V: A K-major, B MN-major (bit 16), N = D.
+  static constexpr int P_BYTES = AT_BM * 128;               // [128][64 keys]; two per query block
+  static constexpr int TMEM_Q = 0;                          // Q[g]: D/2 columns each (two bf16 a column)
+  static constexpr int TMEM_S = 128;                        // S[g]: 64 columns each
+  static constexpr int TMEM_O = 256;                        // O[g]: D columns each
+  static constexpr int TMEM_COLS = 512;
+  static constexpr size_t SMEM = (size_t)AT_STAGES * KV_BYTES + 4 * P_BYTES + 1024 + 256;
+  // S = Q K^T: both K-major, N = 64.   O += P V: A K-major, B MN-major (bit 16), N = D.
   static constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BN >> 3) << 17) |
                                       ((uint32_t)(AT_BM >> 4) << 24);
   static constexpr uint32_t IDESC_R = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                       ((uint32_t)(D >> 3) << 17) | ((uint32_t)(AT_BM >> 4) << 24);
 };
 
+#ifdef AT_STAMPS
+#define AT_STAMP(buf, slot) \
+  if (stamping && j >= 8 && j < 12) (buf)[slot] = clock64();
+#else
+#define AT_STAMP(buf, slot)
+#endif
+
 template <int DS>
 __global__ void __launch_bounds__(AT_THREADS, 1)
-attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_v, const AttnTcArgs a) {
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const bf16* q_rows, const AttnTcArgs a) {
   using Cfg = AtConfig<DS>;
   constexpr int D = Cfg::D;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* q_s = base;
-  uint8_t* kv_s = q_s + Cfg::Q_BYTES;                       // [stage][K sub-tiles | V sub-tiles]
-  uint8_t* p_s = kv_s + AT_STAGES * Cfg::KV_BYTES;          // [2][P_BYTES]
-  uint64_t* bars = (uint64_t*)(p_s + 2 * Cfg::P_BYTES);
-  uint64_t* q_full = bars;                 // 1
-  uint64_t* kv_full = bars + 1;            // [3]
-  uint64_t* kv_empty = kv_full + AT_STAGES;
-  uint64_t* s_full = kv_empty + AT_STAGES; // [2]
-  uint64_t* s_empty = s_full + 2;
-  uint64_t* p_full = s_empty + 2;
-  uint64_t* p_empty = p_full + 2;
-  uint64_t* r_full = p_empty + 2;
-  uint64_t* r_empty = r_full + 2;
+  uint8_t* kv_s = base;                                     // [stage][K sub-tiles | V sub-tiles]
+  uint8_t* p_s = kv_s + AT_STAGES * Cfg::KV_BYTES;          // [query block][2 buffers][P_BYTES]
+  uint64_t* bars = (uint64_t*)(p_s + 4 * Cfg::P_BYTES);
+  uint64_t* kv_full = bars;                  // [stages]
+  uint64_t* kv_empty = kv_full + AT_STAGES;  // [g][stages]: query block g has read the stage
+  uint64_t* q_full = kv_empty + 2 * AT_STAGES;   // [g]: the block's queries are in tensor memory
+  uint64_t* s_full = q_full + 2;             // [g]
+  uint64_t* s_empty = s_full + 2;            // [g]: the softmax threads hold S in registers
+  uint64_t* p_full = s_empty + 2;            // [g][2]
+  uint64_t* o_done = p_full + 4;             // [g]: the product of tile j has been added to O_g
+  uint64_t* o_final = o_done + 2;            // [g]: the last product has been added to O_g
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
-  __shared__ float xch[6 * AT_BM];   // halves of row maxima (2 tiles x 2 groups) and of l
   volatile int* abort_flag = &abort_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y;
   const int qb = a.n_qblocks - 1 - blockIdx.x;   // heavy blocks first
 
-  // which sequence does this query block belong to?
+  // which sequence does this pair of query blocks belong to?
   int seq = 0, first_block = 0, q_len = 0;
   for (; seq < a.n_seqs; ++seq) {
     q_len = a.cu_q[seq + 1] - a.cu_q[seq];
-    const int nb = (q_len + AT_BM - 1) / AT_BM;
+    const int nb = (q_len + 2 * AT_BM - 1) / (2 * AT_BM);
     if (qb < first_block + nb) break;
     first_block += nb;
   }
   if (seq >= a.n_seqs) return;
-  const int q0 = (qb - first_block) * AT_BM;
-  const int rows = min(AT_BM, q_len - q0);
+  const int q0 = (qb - first_block) * 2 * AT_BM;
+  const int rows = min(2 * AT_BM, q_len - q0);          // rows of the pair
   const int tok0 = a.cu_q[seq] + q0;
   const int slot = a.slots[seq];
   const size_t tok_stride = (size_t)a.nq * D;
@@ -139,26 +161,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     return;
   }
   const int kv_len = a.kv_len[seq];
-  const int pos0 = kv_len - q_len + q0;
+  const int pos0 = kv_len - q_len + q0;                 // position of the pair's first row
   const int kvh = h / (a.nq / a.nkv);
   const int* table = a.block_table + (size_t)slot * a.max_pages;
-  const int key_hi = pos0 + rows - 1;
+  const bool has_b = rows > AT_BM;
+  const int rows_a = min(rows, AT_BM), rows_b = rows - AT_BM;
   const int key_lo = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;
-  const int tile_lo = key_lo / AT_BN, n_tiles = key_hi / AT_BN - tile_lo + 1;
+  const int tile_lo = key_lo / AT_BN;
+  // tiles each query block needs (both start at tile_lo; A needs fewer at the end)
+  const int n_a = (pos0 + rows_a - 1) / AT_BN - tile_lo + 1;
+  const int n_b = has_b ? (pos0 + rows - 1) / AT_BN - tile_lo + 1 : 0;
+  const int n_tiles = has_b ? n_b : n_a;
+#ifdef AT_STAMPS
+  long long* stamp_buf = (long long*)(a.error + 64);
+#endif
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
     for (int s = 0; s < AT_STAGES; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
+      mbar_init(&kv_empty[AT_STAGES + s], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 8);   // one arrival per softmax warp
-      mbar_init(&p_full[i], 8);
-      mbar_init(&p_empty[i], 1);
-      mbar_init(&r_full[i], 1);
-      mbar_init(&r_empty[i], 8);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&q_full[g], 4);    // one arrival per softmax warp of the group
+      mbar_init(&s_full[g], 1);
+      mbar_init(&s_empty[g], 4);
+      mbar_init(&o_done[g], 1);
+      mbar_init(&o_final[g], 1);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&p_full[i], 4);
     }
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -179,12 +211,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      mbar_expect_tx(q_full, Cfg::Q_BYTES);
-      for (int ds = 0; ds < DS; ++ds)
-        tma_load_2d(q_s + ds * (AT_BM * 128), &map_q, h * D + ds * 64, tok0, q_full);
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j % AT_STAGES;
-        if (!mbar_wait(&kv_empty[s], (((uint32_t)(j / AT_STAGES)) & 1) ^ 1, abort_flag)) {
+        // the tile that held this stage has been read by the query blocks that needed it
+        const uint32_t par = (((uint32_t)(j / AT_STAGES)) & 1) ^ 1;
+        bool freed = j - AT_STAGES >= n_a || mbar_wait(&kv_empty[s], par, abort_flag);
+        freed = freed && (j - AT_STAGES >= n_b || mbar_wait(&kv_empty[AT_STAGES + s], par, abort_flag));
+        if (!freed) {
           if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_AT_TIMEOUT);
           *abort_flag = 1;
           break;
@@ -200,183 +233,281 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       pdl_launch_dependents();
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 10) {
     // ------------------------------------------------------------------ MMA issue
-    if (lane == 0) {
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      auto issue_r = [&](int i) -> bool {   // R_i = P_i V_i
-        const int b = i & 1, s = i % AT_STAGES;
-        if (!mbar_wait(&p_full[b], ((uint32_t)(i >> 1)) & 1, abort_flag)) return false;
-        if (!mbar_wait(&r_empty[b], (((uint32_t)(i >> 1)) & 1) ^ 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t pa = smem_u32(p_s + b * Cfg::P_BYTES);
-        const uint32_t va = smem_u32(kv_s + (size_t)s * Cfg::KV_BYTES + DS * Cfg::SUB_BYTES);
-        const uint64_t dp = make_smem_desc(pa);
-        const uint64_t dv = make_smem_desc_mn(va, Cfg::SUB_BYTES);
-        const uint32_t tr = tmem_base + Cfg::TMEM_R + b * D;
-#pragma unroll
-        for (int k = 0; k < AT_BN / 16; ++k)   // 16 keys: 32 bytes of a P row, 2 key groups of V
-          tc_mma(tr, dp + 2 * k, dv + (uint64_t)((2 * 1024) >> 4) * k, Cfg::IDESC_R, k > 0 ? 1u : 0u);
-        tc_commit(&r_full[b]);
-        tc_commit(&kv_empty[s]);   // K_i was read by S_i, V_i by R_i: the stage is free
-        tc_commit(&p_empty[b]);
-        return true;
-      };
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int b = j & 1, s = j % AT_STAGES;
-        ok = mbar_wait(&kv_full[s], ((uint32_t)(j / AT_STAGES)) & 1, abort_flag) &&
-             mbar_wait(&s_empty[b], (((uint32_t)(j >> 1)) & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t qa = smem_u32(q_s);
-        const uint32_t ka = smem_u32(kv_s + (size_t)s * Cfg::KV_BYTES);
-        const uint32_t ts = tmem_base + Cfg::TMEM_S + b * AT_BN;
-#pragma unroll
-        for (int ds = 0; ds < DS; ++ds) {
-          const uint64_t dq = make_smem_desc(qa + ds * (AT_BM * 128));
-          const uint64_t dk = make_smem_desc(ka + ds * Cfg::SUB_BYTES);
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma(ts, dq + 2 * k, dk + 2 * k, Cfg::IDESC_S, (ds > 0 || k > 0) ? 1u : 0u);
+    // One warp per query block.  The whole warp walks an event loop: three lanes
+    // test the three barriers that the next products wait for, all at once, a
+    // ballot tells every lane what may be issued, and each burst of instructions
+    // is predicated on an elected lane (no branch that only one lane takes).
+    const int g = warp == 1 ? 0 : 1;
+    const int n_mine = g ? n_b : n_a;
+    int s_next = 0;              // next tile whose S_g is to be issued
+    int o_next = 0;              // next tile whose P_g V is to be issued
+    bool ok = true;
+    unsigned long long idle_since = 0;
+    int idle_rounds = 0;
+#ifdef AT_STAMPS
+    const bool stamping = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
+    int n_stamp = 0;
+    long long* ev_buf = stamp_buf + 64 + g * 96;
+#endif
+    const uint32_t tq = tmem_base + Cfg::TMEM_Q + g * (D / 2);
+    const uint32_t ts = tmem_base + Cfg::TMEM_S + g * AT_BN;
+    const uint32_t to = tmem_base + Cfg::TMEM_O + g * D;
+    while (o_next < n_mine) {
+      // lane 0: K/V of the tile S_g wants; lane 1: Q_g in place (first tile) or S_g
+      // free; lane 2: P_g written.  Branch-free: one test instruction.
+      bool mine = true;
+      {
+        uint64_t* bar = &kv_full[s_next % AT_STAGES];
+        uint32_t par = ((uint32_t)(s_next / AT_STAGES)) & 1;
+        bool need = s_next < n_mine;
+        if (lane == 1) {
+          bar = s_next == 0 ? &q_full[g] : &s_empty[g];
+          par = s_next == 0 ? 0u : ((((uint32_t)s_next) & 1) ^ 1);
         }
-        tc_commit(&s_full[b]);
-        if (j >= 1) ok = issue_r(j - 1);
+        if (lane == 2) {
+          bar = &p_full[g * 2 + (o_next & 1)];
+          par = ((uint32_t)(o_next >> 1)) & 1;
+          need = true;
+        }
+        if (need && lane < 3) mine = mbar_test(bar, par);
       }
-      if (ok) ok = issue_r(n_tiles - 1);
-      if (!ok) {
-        if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_AT_TIMEOUT);
-        *abort_flag = 1;
+      const uint32_t ready = __ballot_sync(0xffffffffu, mine);
+      bool issued = false;
+      tc_fence_after();
+      // O_g += P_g V of the next tile
+      if (o_next < s_next && (ready >> 2 & 1)) {
+        const int t = o_next;
+        const uint32_t pa = smem_u32(p_s + (g * 2 + (t & 1)) * Cfg::P_BYTES);
+        const uint32_t va = smem_u32(kv_s + (size_t)(t % AT_STAGES) * Cfg::KV_BYTES + DS * Cfg::SUB_BYTES);
+        // four products of 16 keys: 32 bytes of a P row, 2 key groups of V each
+        static_assert(AT_BN == 64, "one burst covers a key tile");
+        tc_mma_burst4_w<true>(to, make_smem_desc(pa), make_smem_desc_mn(va, Cfg::SUB_BYTES), 2,
+                              (2 * 1024) >> 4, Cfg::IDESC_R, t > 0 ? 1u : 0u, &o_done[g]);
+        // K_t and V_t go back to the producer when the products so far are done
+        tc_commit_w(&kv_empty[g * AT_STAGES + t % AT_STAGES]);
+        if (t == n_mine - 1) tc_commit_w(&o_final[g]);
+        o_next = t + 1;
+        issued = true;
+#ifdef AT_STAMPS
+        if (stamping && n_stamp < 96 && t >= 8) ev_buf[n_stamp++] = (clock64() << 20) | (t << 8) | (g << 4) | 2;
+#endif
+      }
+      // S_g of the next tile = Q_g K^T.  Not before the product of tile t-2 has been
+      // issued: the softmax threads take a complete S_t to mean that the P buffer of
+      // tile t-2 has been read, and that O_g holds all but the last product.
+      if (s_next < n_mine && o_next + 1 >= s_next && (ready & 1) && (ready >> 1 & 1)) {
+        const int t = s_next;
+        const uint32_t ka = smem_u32(kv_s + (size_t)(t % AT_STAGES) * Cfg::KV_BYTES);
+        // per product 16 elements of head_dim: 8 columns of Q, 32 bytes of a K row
+        if (DS == 1) {
+          tc_mma_ta_burst4_w<true>(ts, tq, make_smem_desc(ka), 2, Cfg::IDESC_S, 0u, &s_full[g]);
+        } else {
+#pragma unroll
+          for (int ds = 0; ds < DS; ++ds) {
+            const uint64_t dk = make_smem_desc(ka + ds * Cfg::SUB_BYTES);
+            if (ds + 1 < DS) tc_mma_ta_burst4_w<false>(ts, tq + ds * 32, dk, 2, Cfg::IDESC_S, ds > 0 ? 1u : 0u, nullptr);
+            else tc_mma_ta_burst4_w<true>(ts, tq + ds * 32, dk, 2, Cfg::IDESC_S, 1u, &s_full[g]);
+          }
+        }
+        s_next = t + 1;
+        issued = true;
+#ifdef AT_STAMPS
+        if (stamping && n_stamp < 96 && t >= 8) ev_buf[n_stamp++] = (clock64() << 20) | (t << 8) | (g << 4) | 1;
+#endif
+      }
+      if (issued) {
+        idle_rounds = 0;
+        continue;
+      }
+      __nanosleep(40);   // leave the issue slots of this scheduler to its softmax warps
+      if (++idle_rounds >= 64) {   // nothing to do for a while: look at the clock
+        const unsigned long long now = now_ns();
+        if (idle_rounds == 64) idle_since = now;
+        const bool stop = *abort_flag || now - idle_since > TC_WAIT_LIMIT_NS;
+        if (__any_sync(0xffffffffu, stop)) {
+          ok = false;
+          break;
+        }
+        idle_rounds = 65;
       }
     }
+    if (!ok && lane == 0) {
+      if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_AT_TIMEOUT);
+      *abort_flag = 1;
+    }
   } else {
-    // ------------------------------------------------------------------ softmax, accumulate, store
-    // Two threads share a query row: group 0 (warps 2-5) owns key columns 0-31 of
-    // every tile and the first half of head_dim, group 1 (warps 6-9) the rest.  The
-    // halves of a row's maximum meet in shared memory once per tile.
-    constexpr int HC = AT_BN / 2, HD = D / 2;
-    const int grp = (warp - 2) >> 2;
-    const int q = warp & 3;                        // the TMEM lanes this warp may read
-    const int r = q * 32 + lane;                   // query row of the block
-    const int pos = pos0 + r;
-    const int hi = r < rows ? pos : -1;            // rows beyond the block see nothing
+    // ------------------------------------------------------------------ softmax and store
+    const int g = (warp - 2) >> 2;                 // query block of this warp (warps 2-9)
+    const int q = warp & 3;                        // the TMEM lanes this warp may touch
+    const int r = q * 32 + lane;                   // query row inside the block
+    const int pos = pos0 + g * AT_BM + r;
+    const int rows_mine = g ? rows_b : rows_a;
+    const int hi = r < rows_mine ? pos : -1;       // rows beyond the step see nothing
     const int lo = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-    float o[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
-    float m = -INFINITY, l = 0.f, corr_prev = 0.f;
+    const uint32_t o_addr = lane_addr + Cfg::TMEM_O + g * D;
+    const uint32_t s_addr = lane_addr + Cfg::TMEM_S + g * AT_BN;
+    const int n_mine = g ? n_b : n_a;
+    float m_used = -INFINITY, l = 0.f;             // base of the exponent (scaled), row sum
     bool ok = true;
+#ifdef AT_STAMPS
+    const bool stamping = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && q == 1;
+#endif
 
     auto wait_warp = [&](uint64_t* bar, uint32_t parity) -> bool {
-      int got = 0;
-      if (lane == 0) got = mbar_wait(bar, parity, nullptr) ? 1 : 0;
-      return __shfl_sync(0xffffffffu, got, 0) != 0;
-    };
-    auto accumulate = [&](int i, float corr) -> bool {   // O = O corr + R_i, this group's half
-      const int b = i & 1;
-      if (!wait_warp(&r_full[b], ((uint32_t)(i >> 1)) & 1)) return false;
-      tc_fence_after();
-      uint32_t v[HD];
-      if constexpr (HD == 64) tc_ld64(lane_addr + Cfg::TMEM_R + b * D + grp * HD, v);
-      else tc_ld32(lane_addr + Cfg::TMEM_R + b * D + grp * HD, v);
-      tc_wait_ld();
-#pragma unroll
-      for (int j = 0; j < HD; ++j) o[j] = o[j] * corr + __uint_as_float(v[j]);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&r_empty[b]);
-      return true;
+      return mbar_wait_warp(bar, parity, nullptr);
     };
 
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    if (n_mine > 0) {
+      // this thread's query row into its lane of tensor memory: 32-bit word c of
+      // the row (elements 2c and 2c+1) is column c
+      const uint4* qrow = reinterpret_cast<const uint4*>(
+          q_rows + ((size_t)(tok0 + g * AT_BM + r) * a.nq + h) * D);
+      const uint32_t q_addr = lane_addr + Cfg::TMEM_Q + g * (D / 2);
+#pragma unroll
+      for (int c0 = 0; c0 < D / 2; c0 += 16) {
+        uint32_t v[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 w = make_uint4(0u, 0u, 0u, 0u);
+          if (r < rows_mine) w = qrow[c0 / 4 + i];   // rows beyond the step are never read
+          v[4 * i] = w.x, v[4 * i + 1] = w.y, v[4 * i + 2] = w.z, v[4 * i + 3] = w.w;
+        }
+        tc_st16(q_addr + c0, v);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_full[g]);
+    }
+
+    for (int j = 0; j < n_mine && ok; ++j) {
       const int b = j & 1;
-      if (!wait_warp(&s_full[b], ((uint32_t)(j >> 1)) & 1)) { ok = false; break; }
+      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 0)
+      if (!wait_warp(&s_full[g], ((uint32_t)j) & 1)) { ok = false; break; }
       tc_fence_after();
-      float s[HC];
+      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 1)
+      float s[AT_BN];
       {
-        uint32_t v[HC];
-        tc_ld32(lane_addr + Cfg::TMEM_S + b * AT_BN + grp * HC, v);
+        uint32_t v[AT_BN];
+        tc_ld64(s_addr, v);
         tc_wait_ld();
 #pragma unroll
-        for (int jj = 0; jj < HC; ++jj) s[jj] = __uint_as_float(v[jj]);
+        for (int jj = 0; jj < AT_BN; ++jj) s[jj] = __uint_as_float(v[jj]);
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[b]);   // S_j is in registers: the buffer is free
+      if (lane == 0) mbar_arrive(&s_empty[g]);   // S is in registers: the next S may be written
+      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 2)
 
-      const int key0 = (tile_lo + j) * AT_BN + grp * HC;
-      // a tile that lies wholly at or below the block's first position (and inside
-      // every row's window) needs no mask
-      const bool need_mask = (tile_lo + j) * AT_BN + AT_BN - 1 > pos0 || a.window > 0 || rows < AT_BM;
+      const int key0 = (tile_lo + j) * AT_BN;
+      // a tile wholly at or below the block's first position (and inside every
+      // row's window) needs no mask
+      const bool need_mask = key0 + AT_BN - 1 > pos0 + g * AT_BM || a.window > 0 || rows_mine < AT_BM;
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < HC; ++c) {
+        for (int c = 0; c < AT_BN; ++c) {
           const int key = key0 + c;
           if (key < lo || key > hi) s[c] = -INFINITY;
         }
       }
-      // row maximum of the raw scores (the scale is positive), four chains
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < HC; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      xch[(b * 2 + grp) * AT_BM + r] = mx;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      mx = fmaxf(mx, xch[(b * 2 + (grp ^ 1)) * AT_BM + r]) * a.scale_log2;
-      const float m_new = fmaxf(m, mx);
-      const float mbase = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = (m == -INFINITY) ? 0.f : fast_exp2(m - mbase);
-      m = m_new;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[HC / 2];
+      for (int c = 0; c < AT_BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
+
+      // raise the base only when the maximum outgrew it by 2^8 (or on the first keys)
+      float factor = 1.0f;
+      const bool raise = mx > m_used + 8.0f;       // also true when m_used is -inf and mx is finite
+      if (raise) {
+        factor = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - mx);
+        m_used = mx;
+      }
+      // rows of O that already hold products must be rescaled; the load and store of
+      // tensor memory are warp-wide, so the warp does it when any lane has to
+      const bool rescale = __any_sync(0xffffffffu, raise && j > 0 && factor != 0.f);
+      if (rescale) {
+        // S_j is complete, so the product of tile j-2, issued before it, is too:
+        // o_done is at most one phase behind
+
+        if (!wait_warp(&o_done[g], ((uint32_t)(j - 1)) & 1)) { ok = false; break; }
+        tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < HC; c += 2) {
+        for (int c0 = 0; c0 < D; c0 += 16) {
+          uint32_t v[16];
+          tc_ld16(o_addr + c0, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int jj = 0; jj < 16; ++jj) v[jj] = __float_as_uint(__uint_as_float(v[jj]) * factor);
+          tc_st16(o_addr + c0, v);
+        }
+        tc_wait_st();
+        tc_fence_before();
+      }
+      l *= factor;
+      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 3)
+
+      const float mbase = (m_used == -INFINITY) ? 0.f : m_used;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[AT_BN / 2];
+#pragma unroll
+      for (int c = 0; c < AT_BN; c += 2) {
         const float e0 = fast_exp2(fmaf(s[c], a.scale_log2, -mbase));
         const float e1 = fast_exp2(fmaf(s[c + 1], a.scale_log2, -mbase));
         sum4[(c >> 1) & 3] += e0 + e1;
         pk[c / 2] = pack2(e0, e1);
       }
-      l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));   // this group's share of l
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 4)
 
-      // P_j into shared memory, K-major [128 rows][64 keys] under the 128-byte swizzle
-      if (!wait_warp(&p_empty[b], (((uint32_t)(j >> 1)) & 1) ^ 1)) { ok = false; break; }
+      // P into shared memory, K-major [128 rows][64 keys] under the 128-byte swizzle.
+      // The buffer is free: S_j was issued after the product of tile j-2, which read
+      // this buffer last, and the tensor core completes in order.
+      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 5)
       {
-        uint8_t* prow = p_s + b * Cfg::P_BYTES + r * 128;
+        uint8_t* prow = p_s + (g * 2 + b) * Cfg::P_BYTES + r * 128;
 #pragma unroll
-        for (int c4 = 0; c4 < HC / 8; ++c4) {
-          const int ch = grp * (HC / 8) + c4;
-          const uint4 w = make_uint4(pk[4 * c4], pk[4 * c4 + 1], pk[4 * c4 + 2], pk[4 * c4 + 3]);
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint4 w = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
           *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = w;
         }
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core
+      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 6)
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[b]);
-
-      if (j >= 1) ok = accumulate(j - 1, corr_prev);
-      corr_prev = corr;
+      if (lane == 0) mbar_arrive(&p_full[g * 2 + b]);
+      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 7)
     }
-    if (ok) ok = accumulate(n_tiles - 1, corr_prev);
+
+    // (o_done cannot serve here: P is double-buffered, so o_done may be two phases
+    // behind and a parity wait would pass on the wrong one)
+    if (ok && n_mine > 0) ok = wait_warp(&o_final[g], 0);
     if (!ok) {
       if (lane == 0) {
         atomicCAS(a.error, 0, GB_ERR_AT_TIMEOUT);
         *abort_flag = 1;
       }
-    } else {
-      // the two halves of l meet, then each group stores its half of the row
-      xch[(4 + grp) * AT_BM + r] = l;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      const float inv = 1.0f / (l + xch[(4 + (grp ^ 1)) * AT_BM + r]);
-      if (r < rows) {
-        bf16* orow = a.out + ((size_t)(tok0 + r) * a.nq + h) * D + grp * HD;
+    } else if (n_mine > 0) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      bf16* orow = a.out + ((size_t)(tok0 + g * AT_BM + r) * a.nq + h) * D;
 #pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 8) {
-          uint4 w;
-          w.x = pack2(o[c0] * inv, o[c0 + 1] * inv);
-          w.y = pack2(o[c0 + 2] * inv, o[c0 + 3] * inv);
-          w.z = pack2(o[c0 + 4] * inv, o[c0 + 5] * inv);
-          w.w = pack2(o[c0 + 6] * inv, o[c0 + 7] * inv);
-          *reinterpret_cast<uint4*>(orow + c0) = w;
+      for (int c0 = 0; c0 < D; c0 += 64) {
+        uint32_t v[64];
+        tc_ld64(o_addr + c0, v);          // warp-wide: every lane loads, valid rows store
+        tc_wait_ld();
+        if (r < rows_mine) {
+#pragma unroll
+          for (int c = 0; c < 64; c += 8) {
+            uint4 w;
+            w.x = pack2(__uint_as_float(v[c]) * inv, __uint_as_float(v[c + 1]) * inv);
+            w.y = pack2(__uint_as_float(v[c + 2]) * inv, __uint_as_float(v[c + 3]) * inv);
+            w.z = pack2(__uint_as_float(v[c + 4]) * inv, __uint_as_float(v[c + 5]) * inv);
+            w.w = pack2(__uint_as_float(v[c + 6]) * inv, __uint_as_float(v[c + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c0 + c) = w;
+          }
         }
       }
     }
@@ -394,8 +525,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 template <int DS>
-static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
-                  const AttnTcArgs& a, cudaStream_t s) {
+static int launch(const CUtensorMap& mk, const CUtensorMap& mv, const bf16* q, const AttnTcArgs& a,
+                  cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<DS>,
@@ -405,7 +536,7 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMa
     configured = true;
   }
   return gb_launch(attn_prefill_tc_kernel<DS>, dim3(a.n_qblocks, a.nq), dim3(AT_THREADS),
-                   AtConfig<DS>::SMEM, s, mq, mk, mv, a);
+                   AtConfig<DS>::SMEM, s, mk, mv, q, a);
 }
 
 // q [n_tokens, nq, D]; k_pages and v_pages [n_pages, nkv, 64, D]; bf16.
@@ -420,15 +551,13 @@ GB_EXPORT int gb_attn_prefill_tc(const void* q, const void* k_pages, const void*
     return GB_ERR_BAD_ARG;
   if (page != AT_BN || (D != 64 && D != 128) || a->nq > 65535) return GB_ERR_UNSUPPORTED;
   if (n_pages * a->nkv * AT_BN > 0x7fffffffll) return GB_ERR_UNSUPPORTED;
+  if (((uintptr_t)q & 15) != 0) return GB_ERR_BAD_ARG;   // query rows are read 16 bytes at a time
   if (a->n_qblocks == 0) return 0;
-  CUtensorMap mq, mk, mv;
-  int e = tc_make_map_2d(&mq, q, (uint64_t)n_tokens, (uint64_t)a->nq * D, (uint64_t)a->nq * D * 2,
-                         AT_BM, 64);
-  if (e) return e;
+  CUtensorMap mk, mv;
   const uint64_t kv_rows = (uint64_t)n_pages * a->nkv * AT_BN;
-  e = tc_make_map_2d(&mk, k_pages, kv_rows, (uint64_t)D, (uint64_t)D * 2, AT_BN, 64);
+  int e = tc_make_map_2d(&mk, k_pages, kv_rows, (uint64_t)D, (uint64_t)D * 2, AT_BN, 64);
   if (e) return e;
   e = tc_make_map_2d(&mv, v_pages, kv_rows, (uint64_t)D, (uint64_t)D * 2, AT_BN, 64);
   if (e) return e;
-  return D == 64 ? launch<1>(mq, mk, mv, *a, s) : launch<2>(mq, mk, mv, *a, s);
+  return D == 64 ? launch<1>(mk, mv, (const bf16*)q, *a, s) : launch<2>(mk, mv, (const bf16*)q, *a, s);
 }

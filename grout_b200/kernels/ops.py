@@ -562,7 +562,7 @@ class _AttnTcArgs(ctypes.Structure):
                 ("window", _I), ("n_qblocks", _I), ("scale_log2", _F)]
 
 
-PREFILL_TC_ROWS = 128      # query rows per block of the tcgen05 prefill kernel
+PREFILL_TC_ROWS = 256      # query rows per block of the tcgen05 prefill kernel (two blocks of 128)
 
 
 def attn_prefill_tc_takes(D: int, nq: int, nkv: int, page: int) -> bool:
