@@ -16,7 +16,12 @@
 // partials; these stay 32-bit.)
 #include "attn_mma.cuh"
 
-#define DC_BN 32
+#ifndef DC_BN
+#define DC_BN 32       // keys per tile
+#endif
+#ifndef DC_STAGES
+#define DC_STAGES 2    // tiles of a warp in shared memory (one less in flight)
+#endif
 #define DC_WARPS 2
 #define DC_THREADS (DC_WARPS * 32)
 
@@ -39,8 +44,7 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
   constexpr int D = 16 * DT, LD = D + 8, CHUNKS = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);       // [16][LD]
-  bf16* kv_s = q_s + 16 * LD;                          // per warp: [2 stages][K, V][32][LD]
-  pdl_wait();   // queries and the newest keys are the producer's output
+  bf16* kv_s = q_s + 16 * LD;                          // per warp: [stages][K, V][DC_BN][LD]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int G = a.nq / a.nkv;
@@ -58,8 +62,15 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
   const int t_begin = tile_lo + split * per_split;
   const int t_end = min(tile_lo + n_tiles, t_begin + per_split);
   const bool empty = t_begin >= t_end;   // a padding row, or more splits than tiles
+  // The producer kernel of this step wrote the queries and the key and value of
+  // position kv_len - 1; everything else this block reads (slots, lengths, block
+  // table, older keys) was there before the step.  So the tiles without the
+  // newest key are requested before waiting for the producer, and its last
+  // microseconds overlap the start of the key stream.
+  const int fresh_tile = pos / DC_BN;
 
   if (empty) {
+    pdl_wait();
     if (single) {
       for (int i = tid; i < G * D; i += DC_THREADS)
         a.out[((size_t)seq * a.nq + h0) * D + i] = __float2bfloat16(0.f);
@@ -71,18 +82,8 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
       ml[1] = 0.f;
     }
   } else {
-    // the query tile: G rows, the rest zero
-    {
-      const bf16* qsrc = a.q + ((size_t)seq * a.nq + h0) * D;
-      for (int i = tid; i < 16 * CHUNKS; i += DC_THREADS) {
-        const int r = i / CHUNKS, ch = i % CHUNKS;
-        const bool ok = r < G;
-        cp_async16(q_s + r * LD + ch * 8, ok ? qsrc + r * D + ch * 8 : qsrc, ok);
-      }
-      cp_async_commit();
-    }
     const int* table = a.block_table + (size_t)slot * a.max_pages;
-    bf16* my = kv_s + (size_t)warp * 4 * DC_BN * LD;
+    bf16* my = kv_s + (size_t)warp * DC_STAGES * 2 * DC_BN * LD;
     const int tiles_per_page = a.page / DC_BN;
 
     auto load_tile = [&](int tile, int stage) {
@@ -99,21 +100,43 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
         cp_async16(vd + r * LD + ch * 8, ok ? a.v_pages + base + r * D + ch * 8 : a.v_pages, ok);
       }
     };
-
+    // the first tiles of this warp, then the producer, then the query tile
+    const int first = t_begin + warp;
+    bool early[DC_STAGES - 1];
+#pragma unroll
+    for (int s = 0; s < DC_STAGES - 1; ++s) {
+      const int tile = first + s * DC_WARPS;
+      early[s] = tile < t_end && tile != fresh_tile;
+      if (early[s]) load_tile(tile, s);
+    }
+    pdl_wait();
+    // the query tile: G rows, the rest zero
+    {
+      const bf16* qsrc = a.q + ((size_t)seq * a.nq + h0) * D;
+      for (int i = tid; i < 16 * CHUNKS; i += DC_THREADS) {
+        const int r = i / CHUNKS, ch = i % CHUNKS;
+        const bool ok = r < G;
+        cp_async16(q_s + r * LD + ch * 8, ok ? qsrc + r * D + ch * 8 : qsrc, ok);
+      }
+    }
     WarpAttn<DT> w;
     w.init();
     int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
-    const int first = t_begin + warp;
-    if (first < t_end) load_tile(first, 0);
+#pragma unroll
+    for (int s = 0; s < DC_STAGES - 1; ++s) {   // what had to wait for the producer
+      const int tile = first + s * DC_WARPS;
+      if (!early[s] && tile < t_end) load_tile(tile, s);
+    }
     cp_async_commit();
-    cp_async_wait<1>();   // the query tile (older group) has landed for this thread
+    cp_async_wait<0>();   // the query tile and this warp's first tiles have landed for this thread
     __syncthreads();      // ... and for all threads
     w.load_q(q_s);
     int stage = 0;
-    for (int tile = first; tile < t_end; tile += DC_WARPS, stage ^= 1) {
-      if (tile + DC_WARPS < t_end) load_tile(tile + DC_WARPS, stage ^ 1);
+    for (int tile = first; tile < t_end; tile += DC_WARPS, stage = stage + 1 == DC_STAGES ? 0 : stage + 1) {
+      const int ahead = tile + (DC_STAGES - 1) * DC_WARPS;
+      if (ahead < t_end) load_tile(ahead, stage == 0 ? DC_STAGES - 1 : stage - 1);
       cp_async_commit();
-      cp_async_wait<1>();
+      cp_async_wait<DC_STAGES - 1>();
       __syncwarp();
       const int key0 = tile * DC_BN;
       const bf16* kt = my + (stage * 2 + 0) * DC_BN * LD;
@@ -204,7 +227,7 @@ __global__ void attn_decode_merge_kernel(const float* part_o, const float* part_
 template <int DT>
 static int launch(const DecodeArgs& a, cudaStream_t s) {
   constexpr int D = 16 * DT, LD = D + 8;
-  const size_t kv_bytes = (size_t)DC_WARPS * 4 * DC_BN * LD * sizeof(bf16);
+  const size_t kv_bytes = (size_t)DC_WARPS * DC_STAGES * 2 * DC_BN * LD * sizeof(bf16);
   const size_t red_bytes = (size_t)(2 * DC_WARPS * 16 + DC_WARPS * 16 * D) * sizeof(float);
   const size_t smem = 16 * LD * sizeof(bf16) + (kv_bytes > red_bytes ? kv_bytes : red_bytes);
   static bool configured = false;

@@ -107,114 +107,125 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int n_heads = a.nq + 2 * a.nkv;
-  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
-  if (head >= n_heads) return;
+  const int warps = blockDim.x >> 5;
   constexpr int D = 64 * P, HALF = D / 2;
-  const bf16* src = (const bf16*)a.qkv + ((size_t)t * n_heads + head) * D;
-  const int kind = head < a.nq ? 0 : (head < a.nq + a.nkv ? 1 : 2);
-  // element index of this lane's p-th pair inside a half: 2 * lane + 64 * p  (< HALF)
-  float lo[P][2], hi[P][2];
   constexpr int NP = (P + 1) / 2;   // pairs per half per lane: HALF / 64 rounded up
-  // HALF = 32 P elements per half; a lane takes pairs at 2 * lane + 64 * p while inside it
-#pragma unroll
-  for (int p = 0; p < NP; ++p) {
-    const int j = 2 * lane + 64 * p;
-    if (j < HALF && a.qkv_parts) {
-      const float* ps = a.qkv_parts + ((size_t)t * n_heads + head) * D;
-      float2 l2 = make_float2(0.f, 0.f), h2 = make_float2(0.f, 0.f);
-      for (int k = 0; k < a.n_parts; ++k) {
-        const float2 lk = *reinterpret_cast<const float2*>(ps + (size_t)k * a.part_stride + j);
-        const float2 hk = *reinterpret_cast<const float2*>(ps + (size_t)k * a.part_stride + HALF + j);
-        l2.x += lk.x; l2.y += lk.y; h2.x += hk.x; h2.y += hk.y;
-      }
-      lo[p][0] = l2.x; lo[p][1] = l2.y;
-      hi[p][0] = h2.x; hi[p][1] = h2.y;
-    } else if (j < HALF) {
-      const __nv_bfloat162 l2 = *reinterpret_cast<const __nv_bfloat162*>(src + j);
-      const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(src + HALF + j);
-      lo[p][0] = __low2float(l2); lo[p][1] = __high2float(l2);
-      hi[p][0] = __low2float(h2); hi[p][1] = __high2float(h2);
-    } else {
-      lo[p][0] = lo[p][1] = hi[p][0] = hi[p][1] = 0.f;
-    }
-  }
-  pdl_launch_dependents_if_large();
-  const WT* w = kind == 0 ? (const WT*)a.q_w : (kind == 1 ? (const WT*)a.k_w : nullptr);
-  if (w) {
-    float ss = 0.f;
-#pragma unroll
-    for (int p = 0; p < NP; ++p)
-      ss += lo[p][0] * lo[p][0] + lo[p][1] * lo[p][1] + hi[p][0] * hi[p][0] + hi[p][1] * hi[p][1];
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
-#pragma unroll
-    for (int p = 0; p < NP; ++p) {
-      const int j = 2 * lane + 64 * p;
-      if (j < HALF) {
-        lo[p][0] = lo[p][0] * inv * to_f32<WT>(w[j]);
-        lo[p][1] = lo[p][1] * inv * to_f32<WT>(w[j + 1]);
-        hi[p][0] = hi[p][0] * inv * to_f32<WT>(w[HALF + j]);
-        hi[p][1] = hi[p][1] * inv * to_f32<WT>(w[HALF + j + 1]);
-      }
-    }
-  }
+  // a lane takes the pairs at 2 * lane + 64 * p of each half while they lie inside it
   const int pos = a.token_pos[t];
-  if (kind != 2 && a.inv_freq) {
+  // the rotation of a position is the same for every head of the token: once per warp
+  float sn[NP][2], cs[NP][2];
+  if (a.inv_freq) {
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
       const int j = 2 * lane + 64 * p;
-      if (j < HALF) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        sn[p][e] = 0.f, cs[p][e] = 1.f;
+        if (j < HALF) sincosf((float)pos * a.inv_freq[j + e], &sn[p][e], &cs[p][e]);
+      }
+    }
+  }
+  // heads of this token in turn: few blocks per token when there are many tokens
+  for (int head = blockIdx.y * warps + warp; head < n_heads; head += gridDim.y * warps) {
+    const bf16* src = (const bf16*)a.qkv + ((size_t)t * n_heads + head) * D;
+    const int kind = head < a.nq ? 0 : (head < a.nq + a.nkv ? 1 : 2);
+    float lo[NP][2], hi[NP][2];
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const int j = 2 * lane + 64 * p;
+      if (j < HALF && a.qkv_parts) {
+        const float* ps = a.qkv_parts + ((size_t)t * n_heads + head) * D;
+        float2 l2 = make_float2(0.f, 0.f), h2 = make_float2(0.f, 0.f);
+        for (int k = 0; k < a.n_parts; ++k) {
+          const float2 lk = *reinterpret_cast<const float2*>(ps + (size_t)k * a.part_stride + j);
+          const float2 hk = *reinterpret_cast<const float2*>(ps + (size_t)k * a.part_stride + HALF + j);
+          l2.x += lk.x; l2.y += lk.y; h2.x += hk.x; h2.y += hk.y;
+        }
+        lo[p][0] = l2.x; lo[p][1] = l2.y;
+        hi[p][0] = h2.x; hi[p][1] = h2.y;
+      } else if (j < HALF) {
+        const __nv_bfloat162 l2 = *reinterpret_cast<const __nv_bfloat162*>(src + j);
+        const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(src + HALF + j);
+        lo[p][0] = __low2float(l2); lo[p][1] = __high2float(l2);
+        hi[p][0] = __low2float(h2); hi[p][1] = __high2float(h2);
+      } else {
+        lo[p][0] = lo[p][1] = hi[p][0] = hi[p][1] = 0.f;
+      }
+    }
+    const WT* w = kind == 0 ? (const WT*)a.q_w : (kind == 1 ? (const WT*)a.k_w : nullptr);
+    if (w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int p = 0; p < NP; ++p)
+        ss += lo[p][0] * lo[p][0] + lo[p][1] * lo[p][1] + hi[p][0] * hi[p][0] + hi[p][1] * hi[p][1];
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+#pragma unroll
+      for (int p = 0; p < NP; ++p) {
+        const int j = 2 * lane + 64 * p;
+        if (j < HALF) {
+          lo[p][0] = lo[p][0] * inv * to_f32<WT>(w[j]);
+          lo[p][1] = lo[p][1] * inv * to_f32<WT>(w[j + 1]);
+          hi[p][0] = hi[p][0] * inv * to_f32<WT>(w[HALF + j]);
+          hi[p][1] = hi[p][1] * inv * to_f32<WT>(w[HALF + j + 1]);
+        }
+      }
+    }
+    if (kind != 2 && a.inv_freq) {
+#pragma unroll
+      for (int p = 0; p < NP; ++p) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const float angle = (float)pos * a.inv_freq[j + e];
-          float sn, cs;
-          sincosf(angle, &sn, &cs);
           const float l = lo[p][e], h = hi[p][e];
-          lo[p][e] = l * cs - h * sn;
-          hi[p][e] = h * cs + l * sn;
+          lo[p][e] = l * cs[p][e] - h * sn[p][e];
+          hi[p][e] = h * cs[p][e] + l * sn[p][e];
+        }
+      }
+    }
+    bf16* dst = nullptr;
+    bf16* dst2 = nullptr;
+    if (kind == 0) {
+      dst = (bf16*)a.q_out + ((size_t)t * a.nq + head) * D;
+    } else {
+      const int hh = kind == 1 ? head - a.nq : head - a.nq - a.nkv;
+      if (a.kv_out)
+        dst2 = (bf16*)a.kv_out + ((size_t)t * 2 * a.nkv + (kind == 1 ? hh : a.nkv + hh)) * D;
+      if (a.k_pages) {
+        const int slot = a.slots[a.token_seq[t]];
+        if (slot >= 0) {
+          const int* table = a.block_table + (size_t)slot * a.max_pages;
+          dst = (bf16*)(kind == 1 ? a.k_pages : a.v_pages) + paged_row(table, pos, hh, a.nkv, a.page, D);
+        }
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const int j = 2 * lane + 64 * p;
+      if (j < HALF) {
+        const __nv_bfloat162 l2 = __floats2bfloat162_rn(lo[p][0], lo[p][1]);
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(hi[p][0], hi[p][1]);
+        if (dst) {
+          *reinterpret_cast<__nv_bfloat162*>(dst + j) = l2;
+          *reinterpret_cast<__nv_bfloat162*>(dst + HALF + j) = h2;
+        }
+        if (dst2) {
+          *reinterpret_cast<__nv_bfloat162*>(dst2 + j) = l2;
+          *reinterpret_cast<__nv_bfloat162*>(dst2 + HALF + j) = h2;
         }
       }
     }
   }
-  bf16* dst = nullptr;
-  bf16* dst2 = nullptr;
-  if (kind == 0) {
-    dst = (bf16*)a.q_out + ((size_t)t * a.nq + head) * D;
-  } else {
-    const int hh = kind == 1 ? head - a.nq : head - a.nq - a.nkv;
-    if (a.kv_out)
-      dst2 = (bf16*)a.kv_out + ((size_t)t * 2 * a.nkv + (kind == 1 ? hh : a.nkv + hh)) * D;
-    if (a.k_pages) {
-      const int slot = a.slots[a.token_seq[t]];
-      if (slot >= 0) {
-        const int* table = a.block_table + (size_t)slot * a.max_pages;
-        dst = (bf16*)(kind == 1 ? a.k_pages : a.v_pages) + paged_row(table, pos, hh, a.nkv, a.page, D);
-      }
-    }
-  }
-#pragma unroll
-  for (int p = 0; p < NP; ++p) {
-    const int j = 2 * lane + 64 * p;
-    if (j < HALF) {
-      const __nv_bfloat162 l2 = __floats2bfloat162_rn(lo[p][0], lo[p][1]);
-      const __nv_bfloat162 h2 = __floats2bfloat162_rn(hi[p][0], hi[p][1]);
-      if (dst) {
-        *reinterpret_cast<__nv_bfloat162*>(dst + j) = l2;
-        *reinterpret_cast<__nv_bfloat162*>(dst + HALF + j) = h2;
-      }
-      if (dst2) {
-        *reinterpret_cast<__nv_bfloat162*>(dst2 + j) = l2;
-        *reinterpret_cast<__nv_bfloat162*>(dst2 + HALF + j) = h2;
-      }
-    }
-  }
+  pdl_launch_dependents_if_large();
 }
 
 template <typename WT>
 static int launch_fast(const QkPrepareArgs& a, cudaStream_t stream) {
   const int warps = 4;
   const int n_heads = a.nq + 2 * a.nkv;
-  dim3 grid(a.n_tokens, (n_heads + warps - 1) / warps);
+  // with few tokens one warp per head; with many, a warp walks several heads and
+  // computes the token's rotation once
+  const int per_warp = a.n_tokens >= 1024 ? 6 : (a.n_tokens >= 128 ? 2 : 1);
+  dim3 grid(a.n_tokens, (n_heads + warps * per_warp - 1) / (warps * per_warp));
   switch (a.D / 64) {
     case 1: return gb_launch(qk_prepare_fast_kernel<WT, 1>, grid, dim3(warps * 32), 0, stream, a);
     case 2: return gb_launch(qk_prepare_fast_kernel<WT, 2>, grid, dim3(warps * 32), 0, stream, a);
