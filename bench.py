@@ -218,7 +218,7 @@ def main() -> int:
     # ---- end to end through the Python entry point -----------------------------------
     e2e = None
     if "e2e" in phases:
-        n_new = min(K, 64) + 1
+        n_new = K + 1
         prompts = [prompt() for _ in range(args.batch)]
         eng.generate(prompts, 4, ignore_eos=True)              # warm-up
         outs = eng.generate(prompts, n_new, ignore_eos=True)

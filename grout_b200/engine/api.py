@@ -192,6 +192,71 @@ class Engine:
                              sum(len(t) for _s, t in entries), started)
         return logits
 
+    # -- stepping ahead --------------------------------------------------------
+    class Chosen:
+        """Tokens chosen on the device, on their way to the host: ``dev`` is the
+        int32 device tensor; the copy to pinned memory was queued right behind the
+        kernel that chose them, so ``tolist()`` waits for that copy only and not
+        for work queued since (the step that already runs on these tokens)."""
+
+        def __init__(self, dev: torch.Tensor, host: torch.Tensor):
+            self.dev, self.host = dev, host
+            host[:dev.shape[0]].copy_(dev, non_blocking=True)
+            self.event = torch.cuda.Event()
+            self.event.record()
+
+        def tolist(self) -> List[int]:
+            self.event.synchronize()
+            return self.host[:self.dev.shape[0]].tolist()
+
+    def choose_ahead(self, logits: torch.Tensor, params, draws) -> "Engine.Chosen":
+        """The device sampler's choice for every row, readable later."""
+        if not hasattr(self, "_chosen_ring"):
+            self._chosen_ring = [torch.zeros(max(self.max_batch, 1), dtype=torch.int32).pin_memory()
+                                 for _ in range(4)]
+            self._chosen_turn = 0
+        host = self._chosen_ring[self._chosen_turn]
+        self._chosen_turn = (self._chosen_turn + 1) % len(self._chosen_ring)
+        with torch.cuda.device(self.device):
+            return Engine.Chosen(self.sampler.choose(logits, params, draws), host)
+
+    def can_step_ahead(self, n: int) -> bool:
+        """Whether decode steps of up to ``n`` sequences can take their tokens on
+        the device (they run as captured graphs)."""
+        return bool(self.use_graphs) and self.graphs.get(n) is not None
+
+    def step_ahead(self, entries: Sequence[Tuple[int, int]], chosen: torch.Tensor) -> torch.Tensor:
+        """One decode step whose input tokens are still on the device: entry
+        (slot, r) continues the sequence in ``slot`` with ``chosen[r]``, an int32
+        device tensor (or the handle of ``choose_ahead``) that earlier work on this
+        stream writes.  Nothing waits for the host.  Returns the step's logits, one row per entry in their order
+        (rows beyond them, if any, are padding)."""
+        if not entries:
+            raise ValueError("a step needs at least one sequence")
+        slots = [s for s, _r in entries]
+        if len(set(slots)) != len(slots):
+            raise ValueError("a slot appears twice in one step")
+        graph = self.graphs.get(len(entries))
+        if graph is None or not self.use_graphs:
+            raise ValueError("this many sequences cannot step ahead: ask can_step_ahead first")
+        for slot in slots:
+            self.cache.reserve(slot, 1)
+        self.cache.flush()
+        packed = [(slot, self.cache.length[slot], [0]) for slot in slots]
+        with torch.cuda.device(self.device):
+            logits = graph.run(packed, tokens_from=(getattr(chosen, "dev", chosen),
+                                                    [r for _s, r in entries]))
+        for slot in slots:
+            self.cache.advance(slot, 1)
+        return logits[:len(entries)]
+
+    def rows(self, logits: torch.Tensor, keep: Sequence[int]) -> torch.Tensor:
+        """The given rows of a step's logits, in that order, without waiting."""
+        keep = list(keep)
+        if keep == list(range(keep[0], keep[0] + len(keep))):
+            return logits[keep[0]:keep[0] + len(keep)]
+        return logits[torch.tensor(keep, device=logits.device)]
+
     # -- generation ------------------------------------------------------------
     def default_stop_ids(self) -> Tuple[int, ...]:
         """generation_config.json's eos list replaces config.json's eos
@@ -205,9 +270,13 @@ class Engine:
 
     def generate(self, prompts, max_new_tokens: int = 128, *,
                  sampling: Optional[SamplingParams] = None, stop_ids=None, ignore_eos: bool = False,
-                 device_argmax: bool = True, include_stop: bool = False) -> List[GenerationOutput]:
+                 device_argmax: bool = True, include_stop: bool = False,
+                 look_ahead: bool = True) -> List[GenerationOutput]:
         """prompts: lists of token ids (or ready ``Request`` objects).  Requests
-        are served in batches of unequal prompts; tokens come back as host ints."""
+        are served in batches of unequal prompts; tokens come back as host ints.
+        ``look_ahead`` (with ``device_argmax``): queue each decode step before the
+        tokens of the one before have been read, its input taken on the device; the
+        tokens returned are the same."""
         sampling = (sampling or SamplingParams()).normalised()
         if ignore_eos:
             stops: Tuple[int, ...] = ()               # src/model.rs:1517-1521
@@ -223,7 +292,9 @@ class Engine:
             out = sampler.choose(logits, params, draws)
             return out.tolist() if isinstance(out, torch.Tensor) else out
 
+        ahead = self.choose_ahead if (look_ahead and device_argmax) else None
         loop = GenerationLoop(self, choose, max_batch=self.max_batch,
                               max_tokens=self.cache.max_tokens, max_seq_len=self.max_seq_len,
-                              vocab_size=self.vocab_size, sync=torch.cuda.synchronize)
+                              vocab_size=self.vocab_size, sync=torch.cuda.synchronize,
+                              choose_ahead=ahead)
         return loop.run(requests)

@@ -12,6 +12,16 @@ The loop talks to the model only through ``open_sequence`` / ``step`` /
 ``close_sequence`` and a chooser, so its decisions can be tested with a scripted
 stand-in and no GPU.  (The reference's loop is ``Qwen3Engine::generate``,
 src/model.rs:1979-2196, for one request.)
+
+Looking ahead.  Reading a step's tokens on the host and only then queueing the
+next step leaves the GPU idle for the host's share of a step.  A stepper that
+offers ``can_step_ahead(n)`` and ``step_ahead(entries, chosen)`` lets the loop
+queue the next step first, its input tokens taken on the device from the chosen
+tokens of this one, and read the tokens while it runs.  Who goes on is then
+decided before the tokens are known: a request that has budget left takes part
+in the next step, and if its token turns out to be a stop token that step was
+run for nothing for its row (its slot is given back as usual, and nothing of the
+row is returned).  The tokens that come back are the same either way.
 """
 from __future__ import annotations
 
@@ -105,8 +115,13 @@ class GenerationLoop:
 
     def __init__(self, stepper, choose: Callable, *, max_batch: int, max_tokens: int,
                  max_seq_len: int, vocab_size: int, clock: Callable[[], float] = time.perf_counter,
-                 sync: Callable[[], None] = lambda: None):
+                 sync: Callable[[], None] = lambda: None, choose_ahead: Optional[Callable] = None):
+        """``choose_ahead(logits, params, draws)``: like ``choose`` but returns at
+        once with a handle ``h`` for which ``stepper.step_ahead(entries, h)`` can take
+        its tokens and ``h.tolist()`` gives them to the host.  With it, and a stepper
+        that can step ahead, the loop looks ahead (see the module's text)."""
         self.stepper, self.choose = stepper, choose
+        self.choose_ahead = choose_ahead
         self.max_batch, self.max_tokens = max_batch, max_tokens
         self.max_seq_len, self.vocab_size = max_seq_len, vocab_size
         self.clock, self.sync = clock, sync
@@ -123,6 +138,66 @@ class GenerationLoop:
         return outputs  # type: ignore[return-value]
 
     def _run_batch(self, requests, batch: List[int], outputs) -> None:
+        ahead = getattr(self.stepper, "can_step_ahead", None)
+        if self.choose_ahead is not None and ahead is not None and ahead(len(batch)):
+            self._run_batch_ahead(requests, batch, outputs)
+        else:
+            self._run_batch_in_turn(requests, batch, outputs)
+
+    def _run_batch_ahead(self, requests, batch: List[int], outputs) -> None:
+        t0 = self.clock()
+        slots = {i: self.stepper.open_sequence() for i in batch}
+        generated = {i: [] for i in batch}
+        reason = {}
+        draws = {i: DrawStream(requests[i].sampling.seed if requests[i].sampling.seed is not None
+                               else 0, i) for i in batch}
+        live = list(batch)          # row r of ``logits`` belongs to live[r]
+        try:
+            logits = self.stepper.step([(slots[i], list(requests[i].prompt)) for i in live],
+                                       [[len(requests[i].prompt) - 1] for i in live])
+            self.steps_run += 1
+            t_prompt = None
+            while True:
+                params = [requests[i].sampling for i in live]
+                us = [0.0 if p.greedy else draws[i].next() for i, p in zip(live, params)]
+                chosen = self.choose_ahead(logits, params, us)
+                # whoever has budget left after this token takes part in the next step
+                going = [(r, i) for r, i in enumerate(live)
+                         if len(generated[i]) + 1 < requests[i].max_new_tokens]
+                nxt = None
+                if going:
+                    nxt = self.stepper.step_ahead([(slots[i], r) for r, i in going], chosen)
+                    self.steps_run += 1
+                tokens = [int(t) for t in chosen.tolist()]     # waits for this step only
+                if t_prompt is None:
+                    t_prompt = self.clock()
+                for i, tok in zip(live, tokens):
+                    r = requests[i]
+                    if tok in r.stop_ids:
+                        if r.include_stop:
+                            generated[i].append(tok)
+                        reason[i] = "stop"
+                    else:
+                        generated[i].append(tok)
+                        if len(generated[i]) >= r.max_new_tokens:
+                            reason[i] = "length"
+                    if i in reason:
+                        self.stepper.close_sequence(slots.pop(i))
+                keep = [k for k, (_r, i) in enumerate(going) if i not in reason]
+                if not keep:
+                    break
+                live = [going[k][1] for k in keep]
+                logits = nxt if len(keep) == len(going) else self.stepper.rows(nxt, keep)
+            self.sync()
+            t_end = self.clock()
+        finally:
+            for s in slots.values():
+                self.stepper.close_sequence(s)
+        for i in batch:
+            outputs[i] = GenerationOutput(generated[i], len(requests[i].prompt), len(generated[i]),
+                                          reason[i], t_prompt - t0, t_end - t_prompt, t_end - t0)
+
+    def _run_batch_in_turn(self, requests, batch: List[int], outputs) -> None:
         t0 = self.clock()
         slots = {i: self.stepper.open_sequence() for i in batch}
         generated = {i: [] for i in batch}

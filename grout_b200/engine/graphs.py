@@ -104,12 +104,24 @@ class DecodeGraph:
         self.kernels_per_replay = ops.launch_count() - before   # this library's kernels in the graph
         self.graph = g
 
-    def run(self, entries) -> torch.Tensor:
+    def run(self, entries, tokens_from=None) -> torch.Tensor:
         """entries: (slot, start, [token]) of the live sequences, at most n.
-        Returns logits [n, vocab]; rows beyond the live sequences are padding."""
+        Returns logits [n, vocab]; rows beyond the live sequences are padding.
+        ``tokens_from`` = (int32 device tensor, rows): the token of entry k is
+        ``tensor[rows[k]]``, copied on the device after the staging copy, so that
+        the step can be queued before the host has seen the tokens."""
         if self.graph is None:
             self._capture()
         self._fill(entries)
+        if tokens_from is not None:
+            chosen, rows = tokens_from
+            o, _cnt = self.off["tokens"]
+            dst = self.dev[o:o + len(rows)]
+            if list(rows) == list(range(len(rows))):
+                dst.copy_(chosen[:len(rows)], non_blocking=True)
+            else:
+                idx = torch.tensor(list(rows), device=self.device)
+                torch.index_select(chosen, 0, idx, out=dst)
         self.graph.replay()
         return self.logits
 

@@ -49,6 +49,38 @@ def test_more_requests_than_slots_are_served_batch_after_batch(model_dirs, plain
     assert eng.cache.slots.n_held == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_looking_ahead_changes_no_token(model_dirs, dtype):
+    """Queueing a step before the host has read the tokens of the one before
+    (their input taken on the device) returns what stepping in turn returns:
+    unequal budgets, stop tokens at different places, sampled and greedy rows,
+    more requests than slots."""
+    from grout_b200.engine.generate import Request
+    from grout_b200.sampling import SamplingParams
+    eng = _engine(model_dirs, "B", dtype)
+    prompts = [random_tokens(n, 384, 760 + n) for n in (2, 9, 33, 64, 5, 17)]
+    free = eng.generate(prompts, 14, ignore_eos=True, look_ahead=False)
+    stops = (free[0].token_ids[3], free[2].token_ids[1], free[4].token_ids[13])
+    reqs = [Request(p, budget, SamplingParams(True, t, k, 0.9, seed=11 + i).normalised()
+                    if t else SamplingParams().normalised(), stops)
+            for i, (p, budget, t, k) in enumerate(zip(prompts, (14, 1, 9, 14, 14, 2),
+                                                      (0, 0, 0, 0.8, 0, 0.7), (0, 0, 0, 20, 0, 0)))]
+    in_turn = eng.generate(reqs, look_ahead=False)
+    ahead = eng.generate(reqs, look_ahead=True)
+    assert [o.token_ids for o in ahead] == [o.token_ids for o in in_turn]
+    assert [o.finish_reason for o in ahead] == [o.finish_reason for o in in_turn]
+    for i, budget in ((0, 14), (1, 1), (2, 9), (4, 14)):      # the greedy requests
+        want = []
+        for tok in free[i].token_ids[:budget]:
+            if tok in stops:
+                break
+            want.append(tok)
+        assert in_turn[i].token_ids == want
+    assert in_turn[0].finish_reason == "stop" and in_turn[1].finish_reason == "length"
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0 and eng.cache.tokens_held() == 0
+
+
 @pytest.mark.parametrize("device_argmax", [True, False])
 def test_bf16_greedy_choices_are_the_plain_best_within_rounding(model_dirs, plain_weights,
                                                                 device_argmax):

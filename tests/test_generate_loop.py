@@ -148,3 +148,83 @@ def test_draws_are_per_request_and_repeatable():
     assert [s1.next() for _ in range(3)] != [s2.next() for _ in range(3)]
     assert SamplingParams(True, 0.0).normalised().temperature == 1e-5
     assert SamplingParams(False, 0.8).greedy and not SamplingParams(True, 0.8).greedy
+
+
+class AheadScript(Script):
+    """The scripted model with the two extra calls of a stepper that can run a
+    step before the host has read the tokens of the one before."""
+
+    class Chosen:
+        def __init__(self, tokens):
+            self.tokens = tokens
+            self.read = False
+
+        def tolist(self):
+            self.read = True
+            return list(self.tokens)
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.ahead_steps = []
+
+    def can_step_ahead(self, n):
+        return True
+
+    def choose_ahead(self, rows, params, draws):
+        return AheadScript.Chosen(self.choose(rows, params, draws))
+
+    def step_ahead(self, entries, chosen):
+        assert not chosen.read, "the step must be queued before the tokens are read"
+        self.ahead_steps.append([r for _s, r in entries])
+        return self.step([(slot, [chosen.tokens[r]]) for slot, r in entries], [[0] for _ in entries])
+
+    def rows(self, logits, keep):
+        return [logits[k] for k in keep]
+
+
+def _ahead_loop(prompts, script, **kw):
+    st = AheadScript(prompts, script, kw.pop("max_slots", 4))
+    loop = GenerationLoop(st, st.choose, max_batch=kw.pop("max_batch", 4),
+                          max_tokens=kw.pop("max_tokens", 4096), max_seq_len=kw.pop("max_seq_len", 512),
+                          vocab_size=1000, choose_ahead=st.choose_ahead)
+    return st, loop
+
+
+def test_looking_ahead_returns_the_same_tokens():
+    prompts = [[1, 2, 3], [4, 5], [6]]
+    script = [[10, 11, 99, 12, 13], [20, 21, 22, 23, 24], [30, 99, 31, 32, 33]]
+    reqs = [Request(prompts[0], 8, stop_ids=(99,)), Request(prompts[1], 4, stop_ids=(99,)),
+            Request(prompts[2], 5, stop_ids=(99,), include_stop=True)]
+    st0, loop0 = _loop(prompts, script)
+    want = loop0.run(reqs)
+    st, loop = _ahead_loop(prompts, script)
+    outs = loop.run(reqs)
+    assert [o.token_ids for o in outs] == [o.token_ids for o in want]
+    assert [o.finish_reason for o in outs] == [o.finish_reason for o in want]
+    assert outs[0].token_ids == [10, 11] and outs[2].token_ids == [30, 99]
+    # every decode step was queued before its tokens were read; a request that drew a
+    # stop token had already been sent into one more step, which changes nothing returned
+    assert st.steps == [[0, 1, 2], [0, 1, 2], [0, 1, 2], [0, 1]]
+    assert st.ahead_steps == [[0, 1, 2], [0, 1, 2], [0, 1]]
+    assert want and st0.steps == [[0, 1, 2], [0, 1, 2], [0, 1], [1]]   # in turn: no row runs for nothing
+    assert not st.open and sorted(st.free) == [0, 1, 2, 3]
+
+
+def test_looking_ahead_runs_no_step_beyond_a_budget():
+    prompts = [[1, 2], [3]]
+    script = [[10, 11, 12, 13], [20, 21, 22, 23]]
+    st, loop = _ahead_loop(prompts, script)
+    outs = loop.run([Request(prompts[0], 1), Request(prompts[1], 3)])
+    assert outs[0].token_ids == [10] and outs[1].token_ids == [20, 21, 22]
+    assert all(o.finish_reason == "length" for o in outs)
+    assert st.steps == [[0, 1], [1], [1]]          # as without looking ahead
+    assert loop.steps_run == 3 and not st.open
+
+
+def test_looking_ahead_serves_batch_after_batch():
+    prompts = [[i + 1] for i in range(5)]
+    script = [[100 + i, 99] for i in range(5)]
+    st, loop = _ahead_loop(prompts, script, max_batch=2, max_slots=2)
+    outs = loop.run([Request(p, 4, stop_ids=(99,)) for p in prompts])
+    assert [o.token_ids for o in outs] == [[100 + i] for i in range(5)]
+    assert st.max_live <= 2 and not st.open and sorted(st.free) == [0, 1]
