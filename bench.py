@@ -178,9 +178,14 @@ def main() -> int:
         slots = [eng.open_sequence() for _ in range(batch)]
         for i in range(0, batch, 8):                       # prompts go in, eight at a time
             eng.step([(s, prompt()) for s in slots[i:i + 8]])
-        toks = torch.randint(0, V, (warm + steps, batch), generator=g).tolist()
+        # the decode step as generation runs it: tokens chosen on the device (greedy)
+        # feed the next step, which is queued without waiting for the host
+        first = torch.randint(0, V, (batch,), generator=g).tolist()
+        logits = eng.step([(s, [first[j]]) for j, s in enumerate(slots)], [[0]] * batch)
+        greedy = [eng.default_sampling()] * batch
+        entries = [(s, j) for j, s in enumerate(slots)]
         for i in range(warm):
-            ops.argmax(eng.step([(s, [toks[i][j]]) for j, s in enumerate(slots)], [[0]] * batch))
+            logits = eng.step_ahead(entries, eng.choose_ahead(logits, greedy, [0.0] * batch))
         torch.cuda.synchronize()
         clocks = ClockSampler() if sample_clocks else None
         if clocks:
@@ -188,8 +193,8 @@ def main() -> int:
         before = ops.launch_count()
         a, b = ev(), ev()
         a.record()
-        for i in range(warm, warm + steps):
-            ops.argmax(eng.step([(s, [toks[i][j]]) for j, s in enumerate(slots)], [[0]] * batch))
+        for i in range(steps):
+            logits = eng.step_ahead(entries, eng.choose_ahead(logits, greedy, [0.0] * batch))
         b.record()
         torch.cuda.synchronize()
         ms = a.elapsed_time(b)

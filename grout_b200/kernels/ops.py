@@ -188,7 +188,7 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
     if qkv.shape[-1] != (nq + 2 * nkv) * D:
         raise KernelError(f"qkv has {qkv.shape[-1]} columns, expected (nq + 2 nkv) * D = "
                           f"{(nq + 2 * nkv) * D}")
-    w_is_f32 = 0
+    w_is_f32 = int(dt == torch.float32)      # without norm weights: whatever the entry point takes
     for w, nm in ((q_w, "q norm weight"), (k_w, "k norm weight")):
         if w is not None:
             _need(w, nm, ndim=1)

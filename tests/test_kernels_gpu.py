@@ -205,6 +205,22 @@ def test_qk_prepare(dtype, nq, nkv, D, rot):
     assert bool(same[~touched].all())
 
 
+@pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("D", [48, 64])
+def test_qk_prepare_without_norm_and_rotation_copies(dtype, D):
+    """No norm weights and no rotation (an attention without q/k norm whose
+    position encoding is applied elsewhere): heads pass through unchanged, keys
+    and values come back dense and nothing is stored when no pages are given."""
+    dt = DT[dtype]
+    nq, nkv, T = 5, 1, 7
+    qkv = _rand((T, (nq + 2 * nkv) * D), dt, 17)
+    z = torch.zeros(T, dtype=torch.int32, device=DEV)
+    q, kv = _ops().qk_prepare(qkv.to(DEV), nq, nkv, D, token_seq=z, token_pos=z,
+                              slots=torch.zeros(1, dtype=torch.int32, device=DEV), want_kv_out=True)
+    x = qkv.view(T, nq + 2 * nkv, D)
+    assert torch.equal(q.cpu(), x[:, :nq]) and torch.equal(kv.cpu(), x[:, nq:])
+
+
 def test_qk_prepare_skips_padding_rows():
     nq, nkv, D = 4, 2, 32
     pc = Paged([5], nkv, D, torch.bfloat16, 15)
