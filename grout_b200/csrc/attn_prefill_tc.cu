@@ -51,8 +51,6 @@
 
 #define AT_BM 128
 #define AT_BN 64
-#define AT_THREADS 352
-#define AT_STAGES 4
 
 #define GB_ERR_AT_TIMEOUT 111
 
@@ -88,17 +86,22 @@ __device__ __forceinline__ float fast_exp2(float x) {   // 2^x, one MUFU operati
   return y;
 }
 
-template <int DS>   // head_dim = 64 * DS
+template <int DS, int G>   // head_dim = 64 * DS; G query blocks of 128 rows per thread block
 struct AtConfig {
   static constexpr int D = 64 * DS;
+  // G = 2: one block per SM, four K/V stages.  G = 1: a block of half the size, two of
+  // which share an SM (two stages each): finer pieces of work for the SMs to share out
+  // when a step has few query rows, and the two blocks overlap like the two query blocks.
+  static constexpr int STAGES = G == 2 ? 4 : 2;
+  static constexpr int THREADS = G == 2 ? 352 : 192;
   static constexpr int SUB_BYTES = AT_BN * 128;             // one [64 keys][64] sub-tile
   static constexpr int KV_BYTES = 2 * DS * SUB_BYTES;       // K and V of one stage
   static constexpr int P_BYTES = AT_BM * 128;               // [128][64 keys]; two per query block
   static constexpr int TMEM_Q = 0;                          // Q[g]: D/2 columns each (two bf16 a column)
-  static constexpr int TMEM_S = 128;                        // S[g]: 64 columns each
-  static constexpr int TMEM_O = 256;                        // O[g]: D columns each
-  static constexpr int TMEM_COLS = 512;
-  static constexpr size_t SMEM = (size_t)AT_STAGES * KV_BYTES + 4 * P_BYTES + 1024 + 256;
+  static constexpr int TMEM_S = G * 64;                     // S[g]: 64 columns each
+  static constexpr int TMEM_O = G * 128;                    // O[g]: D columns each
+  static constexpr int TMEM_COLS = G * 256;
+  static constexpr size_t SMEM = (size_t)STAGES * KV_BYTES + 2 * G * P_BYTES + 1024 + 256;
   // S = Q K^T: both K-major, N = 64.   O += P V: A K-major, B MN-major (bit 16), N = D.
   static constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_BN >> 3) << 17) |
                                       ((uint32_t)(AT_BM >> 4) << 24);
@@ -113,17 +116,18 @@ struct AtConfig {
 #define AT_STAMP(buf, slot)
 #endif
 
-template <int DS>
-__global__ void __launch_bounds__(AT_THREADS, 1)
+template <int DS, int G>
+__global__ void __launch_bounds__((AtConfig<DS, G>::THREADS), (G == 2 ? 1 : 2))
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const bf16* q_rows, const AttnTcArgs a) {
-  using Cfg = AtConfig<DS>;
+  using Cfg = AtConfig<DS, G>;
+  constexpr int AT_STAGES = Cfg::STAGES;
   constexpr int D = Cfg::D;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* kv_s = base;                                     // [stage][K sub-tiles | V sub-tiles]
   uint8_t* p_s = kv_s + AT_STAGES * Cfg::KV_BYTES;          // [query block][2 buffers][P_BYTES]
-  uint64_t* bars = (uint64_t*)(p_s + 4 * Cfg::P_BYTES);
+  uint64_t* bars = (uint64_t*)(p_s + 2 * G * Cfg::P_BYTES);
   uint64_t* kv_full = bars;                  // [stages]
   uint64_t* kv_empty = kv_full + AT_STAGES;  // [g][stages]: query block g has read the stage
   uint64_t* q_full = kv_empty + 2 * AT_STAGES;   // [g]: the block's queries are in tensor memory
@@ -137,26 +141,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   volatile int* abort_flag = &abort_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y;
-  const int qb = a.n_qblocks - 1 - blockIdx.x;   // heavy blocks first
+  const int h = blockIdx.x;
+#ifdef AT_BLOCK_STAMPS
+  unsigned long long* bst = (unsigned long long*)(a.error + 64) + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8;
+  if (threadIdx.x == 0) { bst[0] = now_ns(); unsigned sm; asm("mov.u32 %0, %smid;" : "=r"(sm)); bst[7] = sm; }
+#define BST(i) bst[i] = now_ns();
+#else
+#define BST(i)
+#endif
+  // Blocks are handed to the SMs in the order of their index, x fastest: the heads
+  // are x and the query blocks y, last (longest) first, so that every head's heavy
+  // blocks start before any light one and the light ones fill the gaps at the end.
+  const int qb = a.n_qblocks - 1 - blockIdx.y;
 
   // which sequence does this pair of query blocks belong to?
   int seq = 0, first_block = 0, q_len = 0;
   for (; seq < a.n_seqs; ++seq) {
     q_len = a.cu_q[seq + 1] - a.cu_q[seq];
-    const int nb = (q_len + 2 * AT_BM - 1) / (2 * AT_BM);
+    const int nb = (q_len + G * AT_BM - 1) / (G * AT_BM);
     if (qb < first_block + nb) break;
     first_block += nb;
   }
   if (seq >= a.n_seqs) return;
-  const int q0 = (qb - first_block) * 2 * AT_BM;
-  const int rows = min(2 * AT_BM, q_len - q0);          // rows of the pair
+  const int q0 = (qb - first_block) * G * AT_BM;
+  const int rows = min(G * AT_BM, q_len - q0);          // rows of the block
   const int tok0 = a.cu_q[seq] + q0;
   const int slot = a.slots[seq];
   const size_t tok_stride = (size_t)a.nq * D;
   if (slot < 0) {   // padding sequence: zeros
     bf16* out = a.out + ((size_t)tok0 * a.nq + h) * D;
-    for (int i = threadIdx.x; i < rows * D; i += AT_THREADS)
+    for (int i = threadIdx.x; i < rows * D; i += Cfg::THREADS)
       out[(size_t)(i / D) * tok_stride + (i % D)] = __float2bfloat16(0.f);
     return;
   }
@@ -164,7 +178,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const int pos0 = kv_len - q_len + q0;                 // position of the pair's first row
   const int kvh = h / (a.nq / a.nkv);
   const int* table = a.block_table + (size_t)slot * a.max_pages;
-  const bool has_b = rows > AT_BM;
+  const bool has_b = G == 2 && rows > AT_BM;
   const int rows_a = min(rows, AT_BM), rows_b = rows - AT_BM;
   const int key_lo = (a.window > 0 && pos0 - a.window + 1 > 0) ? pos0 - a.window + 1 : 0;
   const int tile_lo = key_lo / AT_BN;
@@ -189,7 +203,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       mbar_init(&o_done[g], 1);
       mbar_init(&o_final[g], 1);
     }
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 4; ++i) {   // (with one query block the second half is unused)
       mbar_init(&p_full[i], 4);
     }
     abort_s = 0;
@@ -207,6 +221,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
   pdl_wait();
+  if (threadIdx.x == 0) { BST(1) }
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -313,6 +328,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         s_next = t + 1;
         issued = true;
+        if (t == 0 && g == 0 && lane == 0) { BST(2) }
 #ifdef AT_STAMPS
         if (stamping && n_stamp < 96 && t >= 8) ev_buf[n_stamp++] = (clock64() << 20) | (t << 8) | (g << 4) | 1;
 #endif
@@ -483,6 +499,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
     // (o_done cannot serve here: P is double-buffered, so o_done may be two phases
     // behind and a parity wait would pass on the wrong one)
+    if (g == 0 && warp == 2 && lane == 0) { BST(3) }
     if (ok && n_mine > 0) ok = wait_warp(&o_final[g], 0);
     if (!ok) {
       if (lane == 0) {
@@ -514,8 +531,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   }
 
   // ------------------------------------------------------------------ teardown
+  if (warp == 2 && lane == 0) { BST(4) }
   tc_fence_before();
   __syncthreads();
+#ifdef AT_BLOCK_STAMPS
+  if (threadIdx.x == 0) { BST(5) bst[6] = (unsigned long long)n_tiles; }
+#endif
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
@@ -524,32 +545,34 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   }
 }
 
-template <int DS>
+template <int DS, int G>
 static int launch(const CUtensorMap& mk, const CUtensorMap& mv, const bf16* q, const AttnTcArgs& a,
                   cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<DS>,
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<DS, G>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)AtConfig<DS>::SMEM);
+                                         (int)AtConfig<DS, G>::SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return gb_launch(attn_prefill_tc_kernel<DS>, dim3(a.n_qblocks, a.nq), dim3(AT_THREADS),
-                   AtConfig<DS>::SMEM, s, mk, mv, q, a);
+  return gb_launch(attn_prefill_tc_kernel<DS, G>, dim3(a.nq, a.n_qblocks), dim3(AtConfig<DS, G>::THREADS),
+                   AtConfig<DS, G>::SMEM, s, mk, mv, q, a);
 }
 
 // q [n_tokens, nq, D]; k_pages and v_pages [n_pages, nkv, 64, D]; bf16.
 // head_dim 64 or 128 and pages of 64 tokens; anything else is refused
 // (GB_ERR_UNSUPPORTED) and the caller uses another kernel.
+// rows_per_block 128 or 256: a->n_qblocks counts blocks of that many query rows.
 GB_EXPORT int gb_attn_prefill_tc(const void* q, const void* k_pages, const void* v_pages,
                                  const AttnTcArgs* a, int n_tokens, long long n_pages, int D, int page,
-                                 cudaStream_t s) {
+                                 int rows_per_block, cudaStream_t s) {
   if (!q || !k_pages || !v_pages || !a->out || !a->error || a->n_seqs <= 0 || a->nq <= 0 ||
       a->nkv <= 0 || a->nq % a->nkv || a->max_pages <= 0 || a->n_qblocks < 0 || n_tokens <= 0 ||
       n_pages <= 0)
     return GB_ERR_BAD_ARG;
-  if (page != AT_BN || (D != 64 && D != 128) || a->nq > 65535) return GB_ERR_UNSUPPORTED;
+  if (page != AT_BN || (D != 64 && D != 128) || a->n_qblocks > 65535) return GB_ERR_UNSUPPORTED;
+  if (rows_per_block != AT_BM && rows_per_block != 2 * AT_BM) return GB_ERR_BAD_ARG;
   if (n_pages * a->nkv * AT_BN > 0x7fffffffll) return GB_ERR_UNSUPPORTED;
   if (((uintptr_t)q & 15) != 0) return GB_ERR_BAD_ARG;   // query rows are read 16 bytes at a time
   if (a->n_qblocks == 0) return 0;
@@ -559,5 +582,7 @@ GB_EXPORT int gb_attn_prefill_tc(const void* q, const void* k_pages, const void*
   if (e) return e;
   e = tc_make_map_2d(&mv, v_pages, kv_rows, (uint64_t)D, (uint64_t)D * 2, AT_BN, 64);
   if (e) return e;
-  return D == 64 ? launch<1>(mk, mv, (const bf16*)q, *a, s) : launch<2>(mk, mv, (const bf16*)q, *a, s);
+  if (rows_per_block == AT_BM)
+    return D == 64 ? launch<1, 1>(mk, mv, (const bf16*)q, *a, s) : launch<2, 1>(mk, mv, (const bf16*)q, *a, s);
+  return D == 64 ? launch<1, 2>(mk, mv, (const bf16*)q, *a, s) : launch<2, 2>(mk, mv, (const bf16*)q, *a, s);
 }

@@ -436,9 +436,10 @@ def test_fast_attention_refuses_what_it_cannot_do():
                              scale=1.0, max_kv_len=64)
 
 
+@pytest.mark.parametrize("rows_per_block", [128, 256])
 @pytest.mark.parametrize("window", [None, 70])
 @pytest.mark.parametrize("nq,nkv,D", [(8, 1, 128), (6, 2, 64), (16, 4, 128)])
-def test_attn_prefill_tc(nq, nkv, D, window):
+def test_attn_prefill_tc(nq, nkv, D, window, rows_per_block):
     """Both products on the tcgen05 tensor cores.  Rows beyond a sequence's length
     hold large finite values here (the cache zero-fills; NaN there is excluded by
     the kernel's contract)."""
@@ -467,7 +468,7 @@ def test_attn_prefill_tc(nq, nkv, D, window):
         cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
         slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
         kv_len=torch.tensor(lens, dtype=torch.int32, device=DEV), q_lens=tuple(q_lens), page=64,
-        scale=scale, window=window).cpu()
+        scale=scale, window=window, rows_per_block=rows_per_block).cpu()
     ops.check_kernel_errors()
     assert not torch.isnan(got.float()).any()
     for s, (start, n) in enumerate(plan):
