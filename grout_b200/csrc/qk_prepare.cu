@@ -218,6 +218,145 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
   pdl_launch_dependents_if_large();
 }
 
+// The same again for many tokens (a prompt): the kernel above spends some 25
+// instructions an element, which bounds it long before memory does.  Here a lane
+// takes 8 consecutive elements of each half of a head in one 16-byte piece, so a
+// head is D / 16 lanes and a warp prepares 32 / (D / 16) heads at a time; norm
+// weights and the token's rotation are fetched once and reused for every head.
+template <typename WT, int P>
+__global__ void qk_prepare_wide_kernel(const QkPrepareArgs a) {
+  pdl_wait();
+  constexpr int D = 64 * P, HALF = D / 2, LPH = D / 16, HPW = 32 / LPH;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPH, j0 = 8 * (lane % LPH);
+  const int t = blockIdx.x;
+  const int n_heads = a.nq + 2 * a.nkv;
+  const int warps = blockDim.x >> 5;
+  const int pos = a.token_pos[t];
+  // the token's rotation: each angle is computed by one thread of the block and
+  // shared (an accurate sine and cosine cost some forty instructions)
+  __shared__ float sn_s[HALF], cs_s[HALF];
+  for (int j = threadIdx.x; j < HALF; j += blockDim.x) {
+    float sj = 0.f, cj = 1.f;
+    if (a.inv_freq) sincosf((float)pos * a.inv_freq[j], &sj, &cj);
+    sn_s[j] = sj, cs_s[j] = cj;
+  }
+  __syncthreads();
+  float sn[8], cs[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) sn[e] = sn_s[j0 + e], cs[e] = cs_s[j0 + e];
+  float wq[16], wk[16];   // norm weights of this lane's elements: lo half, then hi half
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    wq[e] = a.q_w ? to_f32<WT>(((const WT*)a.q_w)[j0 + e]) : 1.f;
+    wq[8 + e] = a.q_w ? to_f32<WT>(((const WT*)a.q_w)[HALF + j0 + e]) : 1.f;
+    wk[e] = a.k_w ? to_f32<WT>(((const WT*)a.k_w)[j0 + e]) : 1.f;
+    wk[8 + e] = a.k_w ? to_f32<WT>(((const WT*)a.k_w)[HALF + j0 + e]) : 1.f;
+  }
+  int slot = -1;
+  const int* table = nullptr;
+  if (a.k_pages) {
+    slot = a.slots[a.token_seq[t]];
+    if (slot >= 0) table = a.block_table + (size_t)slot * a.max_pages;
+  }
+  const int passes = (n_heads + HPW - 1) / HPW;
+  for (int pass = blockIdx.y * warps + warp; pass < passes; pass += gridDim.y * warps) {
+    const int head = pass * HPW + sub;
+    const bool live = head < n_heads;     // every lane walks the loop: the sums below are warp-wide
+    const bf16* src = (const bf16*)a.qkv + ((size_t)t * n_heads + (live ? head : 0)) * D;
+    const uint4 lo4 = *reinterpret_cast<const uint4*>(src + j0);
+    const uint4 hi4 = *reinterpret_cast<const uint4*>(src + HALF + j0);
+    float lo[8], hi[8];
+    {
+      const uint32_t lw[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, hw[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 l2 = *reinterpret_cast<const __nv_bfloat162*>(&lw[i]);
+        const __nv_bfloat162 h2 = *reinterpret_cast<const __nv_bfloat162*>(&hw[i]);
+        lo[2 * i] = __low2float(l2), lo[2 * i + 1] = __high2float(l2);
+        hi[2 * i] = __low2float(h2), hi[2 * i + 1] = __high2float(h2);
+      }
+    }
+    const int kind = head < a.nq ? 0 : (head < a.nq + a.nkv ? 1 : 2);
+    const bool normed = (kind == 0 && a.q_w) || (kind == 1 && a.k_w);
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (normed) {
+      const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        lo[e] = lo[e] * inv * (kind == 0 ? wq[e] : wk[e]);
+        hi[e] = hi[e] * inv * (kind == 0 ? wq[8 + e] : wk[8 + e]);
+      }
+    }
+    if (kind != 2 && a.inv_freq) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float l = lo[e], h = hi[e];
+        lo[e] = l * cs[e] - h * sn[e];
+        hi[e] = h * cs[e] + l * sn[e];
+      }
+    }
+    uint4 lo_o, hi_o;
+    {
+      uint32_t lw[4], hw[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 l2 = __floats2bfloat162_rn(lo[2 * i], lo[2 * i + 1]);
+        const __nv_bfloat162 h2 = __floats2bfloat162_rn(hi[2 * i], hi[2 * i + 1]);
+        lw[i] = *reinterpret_cast<const uint32_t*>(&l2);
+        hw[i] = *reinterpret_cast<const uint32_t*>(&h2);
+      }
+      lo_o = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+      hi_o = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+    }
+    if (!live) continue;
+    bf16* dst = nullptr;
+    bf16* dst2 = nullptr;
+    if (kind == 0) {
+      dst = (bf16*)a.q_out + ((size_t)t * a.nq + head) * D;
+    } else {
+      const int hh = kind == 1 ? head - a.nq : head - a.nq - a.nkv;
+      if (a.kv_out)
+        dst2 = (bf16*)a.kv_out + ((size_t)t * 2 * a.nkv + (kind == 1 ? hh : a.nkv + hh)) * D;
+      if (table)
+        dst = (bf16*)(kind == 1 ? a.k_pages : a.v_pages) + paged_row(table, pos, hh, a.nkv, a.page, D);
+    }
+    if (dst) {
+      *reinterpret_cast<uint4*>(dst + j0) = lo_o;
+      *reinterpret_cast<uint4*>(dst + HALF + j0) = hi_o;
+    }
+    if (dst2) {
+      *reinterpret_cast<uint4*>(dst2 + j0) = lo_o;
+      *reinterpret_cast<uint4*>(dst2 + HALF + j0) = hi_o;
+    }
+  }
+  pdl_launch_dependents();
+}
+
+template <typename WT>
+static int launch_wide(const QkPrepareArgs& a, cudaStream_t stream) {
+  const int warps = 4;
+  dim3 grid(a.n_tokens, 1);
+  switch (a.D / 64) {
+    case 1: return gb_launch(qk_prepare_wide_kernel<WT, 1>, grid, dim3(warps * 32), 0, stream, a);
+    case 2: return gb_launch(qk_prepare_wide_kernel<WT, 2>, grid, dim3(warps * 32), 0, stream, a);
+    case 4: return gb_launch(qk_prepare_wide_kernel<WT, 4>, grid, dim3(warps * 32), 0, stream, a);
+  }
+  return GB_ERR_UNSUPPORTED;
+}
+
+// 16-byte pieces need 16-byte addresses: all of them are multiples of 8 elements
+// from their tensor's start.
+static bool wide_ok(const QkPrepareArgs& a) {
+  auto al = [](const void* p) { return (((uintptr_t)p) & 15) == 0; };
+  return a.n_tokens >= 128 && !a.qkv_parts && al(a.qkv) && al(a.q_out) && al(a.kv_out) && al(a.k_pages) &&
+         al(a.v_pages);
+}
+
 template <typename WT>
 static int launch_fast(const QkPrepareArgs& a, cudaStream_t stream) {
   const int warps = 4;
@@ -272,6 +411,7 @@ GB_EXPORT int gb_qk_prepare_bf16(const QkPrepareArgs* a, int w_is_f32, cudaStrea
   int e = check(*a);
   if (e) return e;
   if (a->n_tokens == 0) return 0;
+  if (fast_ok(*a) && wide_ok(*a)) return w_is_f32 ? launch_wide<float>(*a, s) : launch_wide<bf16>(*a, s);
   if (fast_ok(*a)) return w_is_f32 ? launch_fast<float>(*a, s) : launch_fast<bf16>(*a, s);
   return w_is_f32 ? launch<bf16, float>(*a, s) : launch<bf16, bf16>(*a, s);
 }

@@ -205,6 +205,43 @@ def test_qk_prepare(dtype, nq, nkv, D, rot):
     assert bool(same[~touched].all())
 
 
+@pytest.mark.parametrize("w32", [False, True])
+@pytest.mark.parametrize("nq,nkv,D", [(6, 2, 64), (5, 1, 128), (3, 3, 256), (7, 2, 48)])
+def test_qk_prepare_of_a_prompt(nq, nkv, D, w32):
+    """Many tokens at once (the path of a prompt, which takes 16 bytes a lane where
+    the sizes allow): 150 tokens of one sequence from position 37 on, over page edges."""
+    dt = torch.bfloat16
+    theta, eps = 10000.0, 1e-6
+    start, T = 37, 150
+    pc = Paged([start + T], nkv, D, dt, 18)
+    qkv = _rand((T, (nq + 2 * nkv) * D), dt, 19)
+    wdt = torch.float32 if w32 else dt
+    q_w = (1 + 0.1 * _rand((D,), torch.float32, 20)).to(wdt)
+    k_w = (1 + 0.1 * _rand((D,), torch.float32, 21)).to(wdt)
+    inv = torch.from_numpy(plain.rope_inv_freq(D, theta))
+    pos = list(range(start, start + T))
+    x = qkv.double().view(T, nq + 2 * nkv, D)
+    cos, sin = plain.rope_cos_sin(pos, D, theta)
+    want_q = plain.apply_rope(plain.rms_norm(x[:, :nq], q_w, eps), cos, sin)
+    want_k = plain.apply_rope(plain.rms_norm(x[:, nq:nq + nkv], k_w, eps), cos, sin)
+    kp, vp = pc.k_pages.to(DEV), pc.v_pages.to(DEV)
+    q, kv = _ops().qk_prepare(
+        qkv.to(DEV), nq, nkv, D, q_w=q_w.to(DEV), k_w=k_w.to(DEV), eps=eps, inv_freq=inv.to(DEV),
+        rot_dim=D, token_seq=torch.zeros(T, dtype=torch.int32, device=DEV),
+        token_pos=torch.tensor(pos, dtype=torch.int32, device=DEV),
+        slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
+        block_table=pc.table.to(DEV), k_pages=kp, v_pages=vp, page=64, want_kv_out=True)
+    tol = dict(atol=6 * _eps(dt), rtol=4 * _eps(dt))
+    assert torch.allclose(q.cpu().double(), want_q, **tol)
+    assert torch.allclose(kv.cpu().double()[:, :nkv], want_k, **tol)
+    assert torch.equal(kv.cpu()[:, nkv:], qkv.view(T, -1, D)[:, nq + nkv:])
+    for r in (0, 26, 27, 90, 91, T - 1):                      # 37 + 27 = 64: the first page edge
+        p = pos[r]
+        pg = int(pc.table[pc.slot_of[0], p // 64])
+        assert torch.allclose(kp[pg, :, p % 64].cpu().double(), want_k[r], **tol)
+        assert torch.equal(vp[pg, :, p % 64].cpu(), qkv.view(T, -1, D)[r, nq + nkv:])
+
+
 @pytest.mark.parametrize("dtype", list(DT))
 @pytest.mark.parametrize("D", [48, 64])
 def test_qk_prepare_without_norm_and_rotation_copies(dtype, D):
