@@ -46,7 +46,12 @@
 // error word (from 64 ints in; the caller must give it 2.5 KB of room): eight
 // per tile for tiles 8-11 of one softmax warp of each query block, then up to 96
 // issue events (clock << 20 | tile << 8 | block << 4 | 1 for S, 2 for PV) of
-// each issuing warp.  A tuning aid; never defined in the product build.
+// each issuing warp.  With -DAT_BLOCK_STAMPS instead, every block writes eight
+// 64-bit words there (index y * gridDim.x + x): %globaltimer at its start, after
+// the wait for the producer kernel, at its first product, after its softmax
+// loop, after its epilogue and at its exit, then its number of key tiles and
+// its SM: this is how the order in which blocks reach the SMs was seen.
+// Tuning aids; never defined in the product build.
 #include "tc_common.cuh"
 
 #define AT_BM 128
