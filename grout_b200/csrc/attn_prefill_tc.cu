@@ -196,6 +196,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #endif
 
   if (threadIdx.x == 0) {
+    tma_prefetch_map(&map_k);
+    tma_prefetch_map(&map_v);
     for (int s = 0; s < AT_STAGES; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);

@@ -130,6 +130,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 
   if (threadIdx.x == 0) {
+    tma_prefetch_map(&map_a);
+    tma_prefetch_map(&map_b);   // used only after the wait for the producer: have it ready by then
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
