@@ -492,6 +492,62 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
     return y
 
 
+class _Tc2Args(ctypes.Structure):
+    _fields_ = [("out", _P), ("error", _P), ("M", _I), ("N", _I), ("K", _I), ("ld", _I),
+                ("out_f32", _I), ("silu", _I), ("bn", _I)]
+
+
+_TC_ERROR_NAMES.update({121: "the pair product's MMA lane waited 2 s for a stage that never arrived",
+                        122: "the pair product's loads waited 2 s for a stage that was never released",
+                        123: "the pair product's epilogue waited 2 s for an accumulator",
+                        124: "the pair product's MMA lane waited 2 s for an accumulator to be drained"})
+
+
+def gemm_tc2_takes(n_out: int, out_dtype) -> bool:
+    """Whether the pair product can store rows of ``n_out`` columns (16 bytes at a time)."""
+    return (n_out * (4 if out_dtype == torch.float32 else 2)) % 16 == 0
+
+
+def gemm_tc2_rounds(M: int, N: int, device) -> float:
+    """How many rounds of 256 x 256 tiles, one per pair of SMs, the product takes."""
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    return tiles / max(1, _sm_count(device) // 2)
+
+
+def gemm_tc2_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
+                  silu_mul: bool = False, tile_cols: int = 0) -> torch.Tensor:
+    """x [M, K] . w [N, K]^T for many rows on pairs of SMs (tcgen05.mma.cta_group::2,
+    tiles of 256 rows and ``tile_cols`` columns: a multiple of 16 up to 256, by
+    default chosen by the kernel's launcher for the shape).  ``silu_mul``: the rows of ``w`` are gate and up rows
+    interleaved in groups of 8 and the result is silu(gate) * up, [M, N / 2]."""
+    _need(x, "activations", torch.bfloat16, 2)
+    _need(w, "weight", torch.bfloat16, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"weight is {tuple(w.shape)} for activations of width {K}")
+    if K % 8:
+        raise KernelError(f"gemm_tc2_bf16 needs an inner size that is a multiple of 8, got {K}")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"output must be bfloat16 or float32, not {out_dtype}")
+    if silu_mul and (N % 16 or out_dtype != torch.bfloat16):
+        raise KernelError("the interleaved gate|up epilogue needs N % 16 == 0 and a bfloat16 output")
+    n_out = N // 2 if silu_mul else N
+    if (n_out * (4 if out_dtype == torch.float32 else 2)) % 16:
+        raise KernelError(f"gemm_tc2_bf16 stores 16 bytes at a time: {n_out} output columns do not allow it")
+    y = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+    if M == 0:
+        return y
+    a = _Tc2Args()
+    a.out, a.error = y.data_ptr(), _tc_error_flag(x.device).data_ptr()
+    a.M, a.N, a.K, a.ld = M, N, K, n_out
+    a.out_f32, a.silu, a.bn = int(out_dtype == torch.float32), int(silu_mul), int(tile_cols)
+    with torch.cuda.device(x.device):
+        _check(_fn("gemm_tc2", "gb_gemm_tc2_bf16", "pppp")(
+            x.data_ptr(), w.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc2_bf16")
+    return y
+
+
 # ---------------------------------------------------------------- fast bf16 attention
 class _PrefillArgs(ctypes.Structure):
     _fields_ = [("q", _P), ("k_pages", _P), ("v_pages", _P), ("block_table", _P), ("cu_q", _P),

@@ -9,9 +9,16 @@ It picks the product by the weight's precision and by the number of rows:
   with the weight rows on the 128-row side of the MMA (``gemm_tc_bf16`` with
   ``swap``), or, for ``decode_kernel = "skinny"``, the mma.sync weight-streaming
   kernel (``gemm_skinny_bf16``).
-* bf16 weight, more rows: by default the library's matrix product, which is where
-  the reference uses a library too (cuBLAS GemmEx, src/cublas.rs:287-307); with
-  ``prefill_kernel = "tc"`` the same tcgen05 kernel in its other orientation.
+* bf16 weight, more rows (a prompt): ``prefill_kernel = "auto"`` takes the product
+  on pairs of SMs (``gemm_tc2_bf16``, tcgen05.mma.cta_group::2) where it is at
+  least as fast as the library's product, which is the fused gate|up product with
+  its SiLU epilogue once it has enough tiles for two rounds, and the library's
+  product elsewhere, where the reference uses a library too (cuBLAS GemmEx,
+  src/cublas.rs:287-307).  ``"pair"`` takes the pair product for everything it
+  can store, ``"tc"`` the single-SM tcgen05 kernel in its other orientation,
+  ``"library"`` the library throughout.  Measured at 2,048 rows (us, library /
+  pair): qkv 50 / 54, o 35 / 52, gate|up 140 + 24 for SiLU / 150 fused, down 73 / 108
+  (o and down are 80 tiles on 74 pairs of SMs: a second round for six tiles).
 """
 from __future__ import annotations
 
@@ -24,7 +31,7 @@ from ..kernels import ops
 
 class Linear:
     decode_kernel = "tc"          # "tc" | "skinny": the product for up to 64 rows
-    prefill_kernel = "library"    # "library" | "tc": the product for more rows
+    prefill_kernel = "auto"       # "auto" | "library" | "pair" | "tc": the product for more rows
 
     def __init__(self, weight: torch.Tensor):
         if weight.dim() != 2:
@@ -37,7 +44,7 @@ class Linear:
     def kernel_modules(self):
         if self.weight.dtype == torch.float32:
             return ("gemm_f32", "elementwise")
-        return ("gemm_tc", "gemm_skinny_bf16")
+        return ("gemm_tc", "gemm_tc2", "gemm_skinny_bf16")
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                  partial_ok: bool = False) -> torch.Tensor:
@@ -60,6 +67,8 @@ class Linear:
                 return ops.gemm_skinny_bf16(x, w, out_dtype)
             if self.prefill_kernel == "tc":
                 return ops.gemm_tc_bf16(x, w, out_dtype, swap=False)
+            if self.prefill_kernel == "pair" and ops.gemm_tc2_takes(self.out_features, out_dtype):
+                return ops.gemm_tc2_bf16(x, w, out_dtype)
         if out_dtype == torch.float32:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
         return torch.mm(x, w.t())
@@ -74,4 +83,10 @@ class Linear:
             if self.decode_kernel == "tc":
                 return ops.gemm_tc_bf16(x, w, x.dtype, swap=True, silu_mul=True)
             return ops.gemm_skinny_bf16(x, w, x.dtype, silu_mul=True)
+        if (interleave == 8 and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+                and self.in_features % 8 == 0 and self.out_features % 32 == 0
+                and (self.prefill_kernel == "pair" or
+                     (self.prefill_kernel == "auto" and
+                      ops.gemm_tc2_rounds(x.shape[0], self.out_features, x.device) >= 2.0))):
+            return ops.gemm_tc2_bf16(x, w, x.dtype, silu_mul=True)
         return ops.silu_mul(self(x), interleave)

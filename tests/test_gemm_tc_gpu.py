@@ -87,3 +87,49 @@ def test_split_out_partials_sum_to_the_product(M, N, K):
     big = ops.gemm_tc_bf16(x.to(DEV)[:, :256].contiguous(), _rand((19456, 256), 82, 0.05).to(DEV),
                            torch.bfloat16, swap=True, split_out=True)
     assert big.dim() == 2
+
+
+# ---- the product on pairs of SMs (tcgen05.mma.cta_group::2)
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K,cols", [(256, 256, 64, 0), (128, 256, 512, 256), (300, 200, 264, 48),
+                                        (2048, 512, 2560, 0), (70, 1000, 96, 144), (513, 136, 4096, 0),
+                                        (1, 8, 8, 0), (2100, 2560, 2560, 0), (600, 1000, 520, 240)])
+def test_pair_product(M, N, K, cols, out_dtype):
+    from grout_b200.kernels import ops
+    x, w = _rand((M, K), 60), _rand((N, K), 61, 0.05)
+    got = ops.gemm_tc2_bf16(x.to(DEV), w.to(DEV), out_dtype, tile_cols=cols)
+    again = ops.gemm_tc2_bf16(x.to(DEV), w.to(DEV), out_dtype, tile_cols=cols)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    want = x.double() @ w.double().T
+    e = 2.0 ** -8 if out_dtype == torch.bfloat16 else 0.0
+    assert got.shape == (M, N) and got.dtype == out_dtype
+    err = (got.double().cpu() - want).abs()
+    bound = 2e-5 * math.sqrt(K) + 2 * e + 2 * e * want.abs()
+    assert bool((err <= bound).all()), (M, N, K, err.max().item())
+    assert torch.equal(got, again)
+
+
+@pytest.mark.parametrize("M", [65, 300, 2048])
+@pytest.mark.parametrize("I,K", [(152, 96), (9728, 2560), (24, 4096)])
+def test_pair_product_silu_epilogue(M, I, K):
+    from grout_b200.kernels import ops
+    x = _rand((M, K), 62)
+    g, u = _rand((I, K), 63, 0.05), _rand((I, K), 64, 0.05)
+    fused = torch.stack([g.view(-1, 8, K), u.view(-1, 8, K)], dim=1).reshape(2 * I, K)
+    got = ops.gemm_tc2_bf16(x.to(DEV), fused.to(DEV), torch.bfloat16, silu_mul=True)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    gd, ud = x.double() @ g.double().T, x.double() @ u.double().T
+    want = gd / (1 + torch.exp(-gd)) * ud
+    assert got.shape == (M, I)
+    err = (got.double().cpu() - want).abs()
+    bound = 8e-5 * math.sqrt(K) + 2.0 ** -7 * want.abs() + 1e-3
+    assert bool((err <= bound).all()), (M, I, K, err.max().item())
+
+
+def test_pair_product_refuses_what_it_cannot_store():
+    from grout_b200.kernels import ops
+    x, w = _rand((4, 64), 65), _rand((12, 64), 66)           # 12 bf16 columns: 24 bytes a row
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tc2_bf16(x.to(DEV), w.to(DEV))

@@ -83,6 +83,27 @@ def test_swiglu_part(dtype):
         assert torch.allclose(got.double().cpu(), want, **TOL[dtype]), rows
 
 
+@pytest.mark.parametrize("kernel", ["auto", "pair", "tc", "library"])
+def test_swiglu_part_with_every_prompt_product(kernel):
+    """The feed-forward of a prompt through each of the products a Linear can be told
+    to use; "pair" fuses SiLU into the gate|up product on pairs of SMs."""
+    from grout_b200.parts import Linear, PartSpec, build_part
+    ff = build_part("feedforward", PartSpec("swiglu", dict(hidden=96, intermediate=208)), _ctx("bfloat16"))
+    p = _params(ff, 12, "bfloat16")
+    _load(ff, p, "bfloat16")
+    ff.gate_up.prefill_kernel = ff.down.prefill_kernel = kernel
+    assert Linear.prefill_kernel == "auto"
+    for rows in (65, 300):
+        x = _rand((rows, 96), 13 + rows).to(torch.bfloat16)
+        got = ff.forward(x.to(DEV), None)
+        if got.dim() == 3:
+            got = got.sum(0)
+        want = plain.swiglu(x.double(), p["gate_proj.weight"], p["up_proj.weight"], p["down_proj.weight"])
+        assert torch.allclose(got.double().cpu(), want, **TOL["bfloat16"]), rows
+    from grout_b200.kernels import ops
+    ops.check_kernel_errors()
+
+
 @pytest.mark.parametrize("window", [None, 24])
 @pytest.mark.parametrize("dtype", list(DT))
 def test_attention_part_prefill_then_decode(dtype, window):
