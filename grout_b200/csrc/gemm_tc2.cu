@@ -32,7 +32,9 @@
 #define T2_BNH 128     // rows of W per block (256 per pair)
 #define T2_BN 256
 #define T2_BK 64
+#ifndef T2_STAGES
 #define T2_STAGES 6
+#endif
 #define T2_THREADS 192  // warp 0: loads; warp 1: MMA issue (first block of the pair); warps 2-5: epilogue
 
 #define GB_ERR_T2_FULL 121
