@@ -358,28 +358,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             // rows 16t..16t+7 of A are gates and 16t+8..16t+15 the matching ups: the up
             // of this lane's gate sits 8 lanes further; out[col_b][feature] = silu(g) * u
             // (the reference's silu_mul_2d_f16, src/kernels.rs:271-296, as an epilogue)
+            // (addresses advance by one row of the output per column: a running pointer per
+            // thread; computing cb * ld afresh for every column went through the uniform
+            // datapath and cost about 100 cycles a column)
+            const int cb0 = tb * BN + c0;
+            const int valid = a.rowsB - cb0;
+            const bool mine = (lane & 15) < 8 && row_a < a.rowsA;
+            const size_t o0 = (size_t)cb0 * a.ld + (size_t)(row_a >> 4) * 8 + (row_a & 7);
+            float* pf = (float*)a.out + o0;
+            bf16* pb = (bf16*)a.out + o0;
+            const size_t ld = (size_t)a.ld;
+            const bool f32 = a.out_f32 != 0;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float up = __shfl_down_sync(0xffffffffu, f[j], 8);
-              const int cb = tb * BN + c0 + j;
-              if ((lane & 15) < 8 && row_a < a.rowsA && cb < a.rowsB) {
-                const size_t o = (size_t)cb * a.ld + (size_t)(row_a >> 4) * 8 + (row_a & 7);
+              if (mine && j < valid) {
                 // bf16 output: the fast exponential and reciprocal are far inside its rounding
                 const float val = f[j] * __frcp_rn(1.0f + __expf(-f[j])) * up;
-                if (a.out_f32) ((float*)a.out)[o] = val;
-                else ((bf16*)a.out)[o] = __float2bfloat16_rn(val);
+                if (f32) *pf = val;
+                else *pb = __float2bfloat16_rn(val);
               }
+              pf += ld;
+              pb += ld;
             }
           } else if (a.transpose_out) {
             // out[col_b][row_a]: lanes hold consecutive row_a, so each j is a coalesced store
             if (row_a < a.rowsA) {
+              const int cb0 = tb * BN + c0;
+              const int valid = a.rowsB - cb0;
+              const size_t ld = (size_t)a.ld;
+              if (a.out_f32) {
+                float* pf = (float*)a.out + (size_t)split_index * a.rowsB * ld + (size_t)cb0 * ld + row_a;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int cb = tb * BN + c0 + j;
-                if (cb < a.rowsB) {
-                  const size_t o = (size_t)cb * a.ld + row_a;
-                  if (a.out_f32) ((float*)a.out)[o + (size_t)split_index * a.rowsB * a.ld] = f[j];
-                  else ((bf16*)a.out)[o] = __float2bfloat16_rn(f[j]);
+                for (int j = 0; j < 16; ++j) {
+                  if (j < valid) *pf = f[j];
+                  pf += ld;
+                }
+              } else {
+                bf16* pb = (bf16*)a.out + (size_t)cb0 * ld + row_a;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  if (j < valid) *pb = __float2bfloat16_rn(f[j]);
+                  pb += ld;
                 }
               }
             }
