@@ -85,11 +85,15 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
     const int* table = a.block_table + (size_t)slot * a.max_pages;
     bf16* my = kv_s + (size_t)warp * DC_STAGES * 2 * DC_BN * LD;
     const int tiles_per_page = a.page / DC_BN;
+    // (a shift where it is a power of two, as with this library's pages of 64: the
+    // division sat in front of every tile's first copy)
+    const int tpp_shift = (tiles_per_page & (tiles_per_page - 1)) == 0 ? __ffs(tiles_per_page) - 1 : -1;
 
     auto load_tile = [&](int tile, int stage) {
-      const int page = table[tile / tiles_per_page];
-      const size_t base =
-          (((size_t)page * a.nkv + kvh) * a.page + (tile % tiles_per_page) * DC_BN) * D;
+      const int pg = tpp_shift >= 0 ? tile >> tpp_shift : tile / tiles_per_page;
+      const int in_page = tile - pg * tiles_per_page;
+      const int page = table[pg];
+      const size_t base = (((size_t)page * a.nkv + kvh) * a.page + in_page * DC_BN) * D;
       bf16* kd = my + (stage * 2 + 0) * DC_BN * LD;
       bf16* vd = my + (stage * 2 + 1) * DC_BN * LD;
       const int valid = kv_len - tile * DC_BN;

@@ -238,7 +238,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issue
     if (lane == 0) {
-      long long it = 0;
+      int s = 0;              // stage and round by counting: every instruction of this
+      uint32_t round = 0;     // lane is on the path of the products
+      bool first = true;
       int seg = 0;
       bool ok = true;
       for (long long u = u_begin; u < u_end && ok; ++seg) {
@@ -254,22 +256,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(ab * BN);
-        for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
-          const int s = (int)(it % STAGES);
-          if (!mbar_wait(&full[s], (uint32_t)(it / STAGES) & 1, abort_flag)) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!mbar_wait(&full[s], round & 1, abort_flag)) {
             if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_TIMEOUT_FULL);
             *abort_flag = 1;
             ok = false;
             break;
           }
           tc_fence_after();
-          if (it == 0) TC_STAMP(4);
+          if (first) {
+            TC_STAMP(4);
+            first = false;
+          }
           const uint32_t sa = smem_u32(tiles_base + (size_t)s * Cfg::STAGE_BYTES);
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + Cfg::A_BYTES);
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; ++k)   // 16 elements = 32 bytes = 2 descriptor units
             tc_mma(tmem_d, da + 2 * k, db + 2 * k, Cfg::IDESC, (kb > kb_lo || k > 0) ? 1u : 0u);
           tc_commit(&empty[s]);   // the stage is free once these MMAs have read it
+          if (++s == STAGES) {
+            s = 0;
+            ++round;
+          }
         }
         if (ok) tc_commit(&acc_full[ab]);
       }

@@ -158,13 +158,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   if (warp == 0) {
     // ------------------------------------------------------------------ loads (both blocks)
     if (lane == 0) {
-      long long it = 0;
       bool ok = true;
+      int s = 0;            // stage and round are kept by counting: this lane's every
+      uint32_t round = 0;   // instruction is on the path of the loads
       for (int tile = cluster; tile < n_tiles && ok; tile += n_clusters) {
         const int tm = tile % tiles_m, tn = tile / tiles_m;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = (int)(it % T2_STAGES);
-          const uint32_t round = (uint32_t)(it / T2_STAGES);
+        for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag)) {
             if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_T2_EMPTY);
             *abort_flag = 1;
@@ -176,6 +175,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           uint8_t* sa = tiles + (size_t)s * T2_STAGE_BYTES;
           tma_load_2d_pair(sa, &map_x, kb * T2_BK, tm * 256 + (int)rank * T2_BM, bar);
           tma_load_2d_pair(sa + T2_A_BYTES, &map_w, kb * T2_BK, tn * bn + (int)rank * bnh, bar);
+          if (++s == T2_STAGES) {
+            s = 0;
+            ++round;
+          }
         }
       }
       pdl_launch_dependents();
@@ -183,7 +186,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue (first block)
     if (rank == 0 && lane == 0) {
-      long long it = 0;
+      int s = 0;
+      uint32_t round = 0;
       int t = 0;
       bool ok = true;
       const uint32_t idesc = T2_IDESC | ((uint32_t)(bn >> 3) << 17);
@@ -196,9 +200,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         }
         tc_fence_after();
         const uint32_t acc = tmem_base + ab * T2_BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = (int)(it % T2_STAGES);
-          if (!mbar_wait(&full[s], (uint32_t)(it / T2_STAGES) & 1, abort_flag)) {
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full[s], round & 1, abort_flag)) {
             if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_T2_FULL);
             *abort_flag = 1;
             ok = false;
@@ -211,6 +214,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           for (int k = 0; k < T2_BK / 16; ++k)
             tc_mma_pair(acc, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           tc_commit_pair(&empty[s]);      // the stage is free in both blocks
+          if (++s == T2_STAGES) {
+            s = 0;
+            ++round;
+          }
         }
         if (ok) tc_commit_pair(&acc_full[ab]);   // both blocks may drain their half of the tile
       }

@@ -11,14 +11,15 @@ It picks the product by the weight's precision and by the number of rows:
   kernel (``gemm_skinny_bf16``).
 * bf16 weight, more rows (a prompt): ``prefill_kernel = "auto"`` takes the product
   on pairs of SMs (``gemm_tc2_bf16``, tcgen05.mma.cta_group::2) where it is at
-  least as fast as the library's product, which is the fused gate|up product with
-  its SiLU epilogue once it has enough tiles for two rounds, and the library's
-  product elsewhere, where the reference uses a library too (cuBLAS GemmEx,
-  src/cublas.rs:287-307).  ``"pair"`` takes the pair product for everything it
-  can store, ``"tc"`` the single-SM tcgen05 kernel in its other orientation,
-  ``"library"`` the library throughout.  Measured at 2,048 rows (us, library /
-  pair): qkv 50 / 54, o 35 / 52, gate|up 140 + 24 for SiLU / 150 fused, down 73 / 108
-  (o and down are 80 tiles on 74 pairs of SMs: a second round for six tiles).
+  least as fast as the library's product, which is when its 256 x 256 tiles fill
+  at least two rounds on the GPU's pairs of SMs (the qkv product and the fused
+  gate|up product with its SiLU epilogue), and the library's product elsewhere,
+  where the reference uses a library too (cuBLAS GemmEx, src/cublas.rs:287-307).
+  ``"pair"`` takes the pair product for everything it can store, ``"tc"`` the
+  single-SM tcgen05 kernel in its other orientation, ``"library"`` the library
+  throughout.  Measured at 2,048 rows (us, library / pair): qkv 50 / 51, o 35 / 48,
+  gate|up 140 + 24 for SiLU / 145 fused, down 73 / 102 (o and down are 80 tiles on
+  74 pairs of SMs: a second round for six tiles).
 """
 from __future__ import annotations
 
@@ -67,7 +68,10 @@ class Linear:
                 return ops.gemm_skinny_bf16(x, w, out_dtype)
             if self.prefill_kernel == "tc":
                 return ops.gemm_tc_bf16(x, w, out_dtype, swap=False)
-            if self.prefill_kernel == "pair" and ops.gemm_tc2_takes(self.out_features, out_dtype):
+            if ops.gemm_tc2_takes(self.out_features, out_dtype) and (
+                    self.prefill_kernel == "pair" or
+                    (self.prefill_kernel == "auto" and
+                     ops.gemm_tc2_rounds(M, self.out_features, x.device) >= 2.0)):
                 return ops.gemm_tc2_bf16(x, w, out_dtype)
         if out_dtype == torch.float32:
             return torch.mm(x, w.t(), out_dtype=torch.float32)
