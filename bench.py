@@ -154,7 +154,7 @@ def main() -> int:
     # ---- prefill of 2,048 tokens ---------------------------------------------------
     p = prompt()
     times = []
-    for i in range(6 if "prefill" in phases else 0):
+    for i in range(9 if "prefill" in phases else 0):      # three to warm up, the median of six
         s = eng.open_sequence()
         torch.cuda.synchronize()
         a, b = ev(), ev()
@@ -163,7 +163,7 @@ def main() -> int:
         b.record()
         torch.cuda.synchronize()
         eng.close_sequence(s)
-        if i >= 2:
+        if i >= 3:
             times.append(a.elapsed_time(b))
     prefill = None
     if times:
