@@ -234,7 +234,7 @@ def main() -> int:
                "d2h_bytes_per_step": 4 * args.batch}
 
     print(json.dumps({
-        "metric": "decode tok/s (Qwen3-4B shape, batch 8, 2,048-token prompts)",
+        "metric": f"decode tok/s (Qwen3-4B shape, batch {args.batch}, 2,048-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
