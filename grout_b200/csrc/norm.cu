@@ -108,22 +108,32 @@ __global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta, cons
   const float* pin = parts ? parts + s * N : nullptr;
   float v[NV_MAX][4];
   float ss = 0.f;
+  // all of a thread's loads first, then the sums: the memory system sees every
+  // request of the row at once
+  float av[NV_MAX][4], dv[NV_MAX][4];
+#pragma unroll
+  for (int j = 0; j < NV_MAX; ++j) {
+    const int i = (threadIdx.x + j * blockDim.x) * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) av[j][e] = dv[j][e] = 0.f;
+    if (i < N) {
+      if (rin) Vec4<float>::load(rin + i, av[j]);
+      if (din) Vec4<T>::load(din + i, dv[j]);
+    }
+  }
 #pragma unroll
   for (int j = 0; j < NV_MAX; ++j) {
     const int i = (threadIdx.x + j * blockDim.x) * 4;
     if (i < N) {
-      float a[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};
-      if (rin) Vec4<float>::load(rin + i, a);
-      if (din) Vec4<T>::load(din + i, d);
       for (int k = 0; k < n_parts; ++k) {
         float pk[4];
         Vec4<float>::load(pin + (size_t)k * part_stride + i, pk);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) d[e] += pk[e];
+        for (int e = 0; e < 4; ++e) dv[j][e] += pk[e];
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        v[j][e] = a[e] + d[e];
+        v[j][e] = av[j][e] + dv[j][e];
         ss += v[j][e] * v[j][e];
       }
       if (rout) Vec4<float>::store(rout + i, v[j]);
