@@ -125,11 +125,19 @@ __global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta, cons
   for (int j = 0; j < NV_MAX; ++j) {
     const int i = (threadIdx.x + j * blockDim.x) * 4;
     if (i < N) {
-      for (int k = 0; k < n_parts; ++k) {
-        float pk[4];
-        Vec4<float>::load(pin + (size_t)k * part_stride + i, pk);
+      for (int k0 = 0; k0 < n_parts; k0 += 4) {   // four at once, added in order
+        float pk[4][4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) dv[j][e] += pk[e];
+        for (int u = 0; u < 4; ++u) {
+          const int k = k0 + u < n_parts ? k0 + u : n_parts - 1;
+          Vec4<float>::load(pin + (size_t)k * part_stride + i, pk[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (k0 + u < n_parts) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dv[j][e] += pk[u][e];
+          }
       }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -186,11 +194,21 @@ __global__ void add_rmsnorm_cluster_kernel(const float* res_in, const T* delta, 
     float a[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};
     if (res_in) Vec4<float>::load(res_in + s * N + i, a);
     if (delta) Vec4<T>::load(delta + s * N + i, d);
-    for (int k = 0; k < n_parts; ++k) {
-      float pk[4];
-      Vec4<float>::load(parts + (size_t)k * part_stride + s * N + i, pk);
+    // four partials are requested at once and then added in order: one at a time, each
+    // load would wait for the one before it to have been added (a round trip to L2 each)
+    for (int k0 = 0; k0 < n_parts; k0 += 4) {
+      float pk[4][4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) d[e] += pk[e];
+      for (int u = 0; u < 4; ++u) {
+        const int k = k0 + u < n_parts ? k0 + u : n_parts - 1;
+        Vec4<float>::load(parts + (size_t)k * part_stride + s * N + i, pk[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (k0 + u < n_parts) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) d[e] += pk[u][e];
+        }
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {

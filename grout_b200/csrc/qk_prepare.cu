@@ -136,10 +136,21 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
       if (j < HALF && a.qkv_parts) {
         const float* ps = a.qkv_parts + ((size_t)t * n_heads + head) * D;
         float2 l2 = make_float2(0.f, 0.f), h2 = make_float2(0.f, 0.f);
-        for (int k = 0; k < a.n_parts; ++k) {
-          const float2 lk = *reinterpret_cast<const float2*>(ps + (size_t)k * a.part_stride + j);
-          const float2 hk = *reinterpret_cast<const float2*>(ps + (size_t)k * a.part_stride + HALF + j);
-          l2.x += lk.x; l2.y += lk.y; h2.x += hk.x; h2.y += hk.y;
+        // four partials are requested at once and then added in order (one at a time, each
+        // load would wait for the one before it to have been added)
+        for (int k0 = 0; k0 < a.n_parts; k0 += 4) {
+          float2 lk[4], hk[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int k = k0 + u < a.n_parts ? k0 + u : a.n_parts - 1;
+            lk[u] = *reinterpret_cast<const float2*>(ps + (size_t)k * a.part_stride + j);
+            hk[u] = *reinterpret_cast<const float2*>(ps + (size_t)k * a.part_stride + HALF + j);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (k0 + u < a.n_parts) {
+              l2.x += lk[u].x; l2.y += lk[u].y; h2.x += hk[u].x; h2.y += hk[u].y;
+            }
         }
         lo[p][0] = l2.x; lo[p][1] = l2.y;
         hi[p][0] = h2.x; hi[p][1] = h2.y;
