@@ -209,20 +209,39 @@ __global__ void attn_decode_merge_kernel(const float* part_o, const float* part_
                                          bf16* __restrict__ out, int n_splits, int D) {
   pdl_launch_dependents_if_small();
   pdl_wait();
+  // Loads are requested eight splits at a time and then used in split order: a loop that
+  // folds one split after the other makes every load wait for the one before it, a round
+  // trip to L2 each, and this kernel is nothing but such loads.
   const size_t p0 = (size_t)blockIdx.x * n_splits;
+  const float2* ml = reinterpret_cast<const float2*>(part_ml) + p0;   // (max, sum) of every split
   float M = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
-  float L = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float m = part_ml[(p0 + s) * 2];
-    if (m != -INFINITY) L += part_ml[(p0 + s) * 2 + 1] * exp2f(m - M);
+  for (int s0 = 0; s0 < n_splits; s0 += 8) {
+    float2 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = ml[s0 + u < n_splits ? s0 + u : n_splits - 1];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) M = fmaxf(M, v[u].x);
   }
   pdl_launch_dependents_if_large();
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float O = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float m = part_ml[(p0 + s) * 2];
-      if (m != -INFINITY) O += part_o[(p0 + s) * D + d] * exp2f(m - M);
+    float L = 0.f, O = 0.f;
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+      float2 v[8];
+      float o[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int sidx = s0 + u < n_splits ? s0 + u : n_splits - 1;
+        v[u] = ml[sidx];
+        o[u] = part_o[(p0 + sidx) * D + d];
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (s0 + u < n_splits && v[u].x != -INFINITY) {
+          const float f = exp2f(v[u].x - M);
+          L += v[u].y * f;
+          O += o[u] * f;
+        }
+      }
     }
     out[(size_t)blockIdx.x * D + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
   }
