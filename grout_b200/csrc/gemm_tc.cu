@@ -25,6 +25,12 @@
 // at the tile's counter, which adds the 32-bit partials (kept in scratch, two
 // slots per block) in block order.  No block waits for another block.
 //
+// Leftover deal (lead_share = S > 0, chosen by the host for wide tiles when there are a
+// few more tiles than blocks): block p owns tile p whole, and the tiles beyond the
+// P-th are cut S ways over K among blocks 0 .. (tiles - P) S - 1, each of which takes
+// its share BEFORE its own tile.  The shares end early and together, so the block that
+// adds them does it while its own tile streams, and no block streams two whole tiles.
+//
 // Every wait on an mbarrier is bounded by a wall-clock limit; when it expires
 // the block records a code in args.error, stops issuing work, waits (bounded)
 // for its copies in flight, frees its tensor memory and returns.
@@ -41,6 +47,18 @@
 #endif
 #ifndef TC_SHARE_64
 #define TC_SHARE_64 4
+#endif
+// Leftover deal: the most shares a leftover tile is cut into.  The block that adds the
+// shares reads them (128 x BN floats each) while its own tile streams; its loads wait
+// behind that stream, so wide tiles take few shares.
+#ifndef TC_LEAD_SHARE_16
+#define TC_LEAD_SHARE_16 10
+#endif
+#ifndef TC_LEAD_SHARE_32
+#define TC_LEAD_SHARE_32 6
+#endif
+#ifndef TC_LEAD_SHARE_64
+#define TC_LEAD_SHARE_64 4
 #endif
 #define TC_BM 128
 #define TC_BK 64
@@ -76,6 +94,18 @@ struct TcArgs {
     if (a.stamps) a.stamps[(size_t)blockIdx.x * 8 + (slot)] = now_ns();      \
   } while (0)
 
+// Stores that are predicated instructions, never a branch.
+__device__ __forceinline__ void st_f32_if(float* p, float v, bool on) {
+  asm volatile("{ .reg .pred q; setp.ne.b32 q, %2, 0; @q st.global.f32 [%0], %1; }" ::"l"(p), "f"(v),
+               "r"((int)on)
+               : "memory");
+}
+__device__ __forceinline__ void st_bf16_if(bf16* p, bf16 v, bool on) {
+  asm volatile("{ .reg .pred q; setp.ne.b32 q, %2, 0; @q st.global.b16 [%0], %1; }" ::"l"(p),
+               "h"(__bfloat16_as_ushort(v)), "r"((int)on)
+               : "memory");
+}
+
 __device__ __forceinline__ int tc_block_of_unit(long long u, long long U, int P) {
   return (int)(((u + 1) * P - 1) / U);
 }
@@ -99,7 +129,7 @@ struct TcConfig {
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const TcArgs a) {
+               const TcArgs a, const int lead_share) {
   using Cfg = TcConfig<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -120,13 +150,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int tiles_a = (a.rowsA + TC_BM - 1) / TC_BM, tiles_b = (a.rowsB + BN - 1) / BN;
   const int kblocks = (a.K + TC_BK - 1) / TC_BK;
   const long long U = (long long)tiles_a * tiles_b * kblocks;
-  long long u_begin = p * U / P, u_end = (p + 1) * U / P;
+  // the units of this block: two ranges of the line, worked in this order (the first is
+  // empty except in the leftover deal)
+  // (scalars, not arrays: an array indexed by the range would live in local memory)
+  long long rb0 = 0, re0 = 0, rb1 = p * U / P, re1 = (p + 1) * U / P;
   int split_index = 0;
   if (a.split_k > 0) {   // block p = tile * S + s takes the s-th share of its tile's k-blocks
     const int tile = p / a.split_k;
     split_index = p - tile * a.split_k;
-    u_begin = (long long)tile * kblocks + (long long)split_index * kblocks / a.split_k;
-    u_end = (long long)tile * kblocks + (long long)(split_index + 1) * kblocks / a.split_k;
+    rb1 = (long long)tile * kblocks + (long long)split_index * kblocks / a.split_k;
+    re1 = (long long)tile * kblocks + (long long)(split_index + 1) * kblocks / a.split_k;
+  } else if (lead_share > 0) {
+    rb1 = (long long)p * kblocks;
+    re1 = rb1 + kblocks;
+    const int n_left = tiles_a * tiles_b - P;
+    if (p < n_left * lead_share) {
+      const int j = p / lead_share, sh = p - j * lead_share;
+      rb0 = (long long)(P + j) * kblocks + (long long)sh * kblocks / lead_share;
+      re0 = (long long)(P + j) * kblocks + (long long)(sh + 1) * kblocks / lead_share;
+    }
   }
 
   if (threadIdx.x == 0) {
@@ -162,7 +204,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
-      const long long n_units = u_end - u_begin;
+      const long long n_units = (re0 - rb0) + (re1 - rb1);
       // The operand that no kernel writes (the weights) is requested for the first
       // ring of stages before this kernel waits for its producer; the other
       // operand (the activations) follows once that kernel has finished.
@@ -171,6 +213,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // a 64-bit unit number for every copy cost this lane some 300 cycles a unit
       struct Cursor {
         int ta, tb, kb;
+        long long left;   // units left in the first range (0: in the second)
       };
       auto cursor_at = [&](long long u) {
         const int tile = (int)(u / kblocks);
@@ -178,9 +221,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         c.kb = (int)(u - (long long)tile * kblocks);
         c.ta = tile % tiles_a;
         c.tb = tile / tiles_a;
+        c.left = 0;
         return c;
       };
+      auto cursor_first = [&]() {
+        if (re0 > rb0) {
+          Cursor c = cursor_at(rb0);
+          c.left = re0 - rb0;
+          return c;
+        }
+        return cursor_at(rb1);
+      };
       auto advance = [&](Cursor& c) {
+        if (c.left > 0 && --c.left == 0) {   // the first range is done: on to the second
+          c = cursor_at(rb1);
+          return;
+        }
         if (++c.kb == kblocks) {
           c.kb = 0;
           if (++c.ta == tiles_a) {
@@ -194,7 +250,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (want_a) tma_load_2d(sa, &map_a, c.kb * TC_BK, c.ta * TC_BM, &full[s]);
         if (want_b) tma_load_2d(sa + Cfg::A_BYTES, &map_b, c.kb * TC_BK, c.tb * BN, &full[s]);
       };
-      Cursor cur = cursor_at(u_begin);
+      Cursor cur = cursor_first();
       for (int i = 0; i < (int)n_early; ++i) {   // first round: every stage is free
         mbar_expect_tx(&full[i], Cfg::STAGE_BYTES);
         issue(cur, i, a.dep_b != 0, a.dep_b == 0);
@@ -202,7 +258,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       }
       pdl_wait();
       TC_STAMP(2);
-      cur = cursor_at(u_begin);
+      cur = cursor_first();
       for (int i = 0; i < (int)n_early; ++i) {
         issue(cur, i, a.dep_b == 0, a.dep_b != 0);
         advance(cur);
@@ -243,7 +299,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       bool first = true;
       int seg = 0;
       bool ok = true;
-      for (long long u = u_begin; u < u_end && ok; ++seg) {
+      for (int rg = 0; rg < 2; ++rg)
+      for (long long u = rg ? rb1 : rb0, u_end = rg ? re1 : re0; u < u_end && ok; ++seg) {
         const int tile = (int)(u / kblocks);
         const int kb_lo = (int)(u - (long long)tile * kblocks);
         const int kb_hi = (int)min((long long)kblocks, kb_lo + (u_end - u));
@@ -252,6 +309,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (!mbar_wait(&acc_empty[ab], (((uint32_t)seg >> 1) & 1) ^ 1, abort_flag)) {
           if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_TIMEOUT_TMEM_EMPTY);
           *abort_flag = 1;
+          ok = false;
           break;
         }
         tc_fence_after();
@@ -290,11 +348,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int et = threadIdx.x - 64;      // 0..127 among the epilogue threads
     int seg = 0;
     bool ok = true;
-    for (long long u = u_begin; u < u_end && ok; ++seg) {
+    for (int rg = 0; rg < 2; ++rg)
+    for (long long u = rg ? rb1 : rb0, u_end = rg ? re1 : re0; u < u_end && ok; ++seg) {
       const int tile = (int)(u / kblocks);
       const int kb_lo = (int)(u - (long long)tile * kblocks);
       const int kb_hi = (int)min((long long)kblocks, kb_lo + (u_end - u));
-      const long long u_seg = u;
       u += kb_hi - kb_lo;
       const int ta = tile % tiles_a, tb = tile / tiles_a;
       const int ab = seg & 1;
@@ -309,6 +367,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           atomicCAS(a.error, 0, GB_ERR_TIMEOUT_TMEM_FULL);
           *abort_flag = 1;
         }
+        ok = false;
         break;
       }
       tc_fence_after();
@@ -319,7 +378,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int p_first = 0, p_last = 0;
       if (!whole) {
         // leave the partial [128][BN] in this block's slot, then see who is last
-        const bool my_first_tile = (int)(u_begin / kblocks) == tile;
+        // slot 0 for the tile this block's own range begins in, slot 1 for its other shared
+        // tile (a range ends in at most one more) and for a share of the leftover deal
+        const bool my_first_tile = rg == 1 && (int)(rb1 / kblocks) == tile;
         float* mine = a.scratch + ((size_t)2 * p + (my_first_tile ? 0 : 1)) * (size_t)(BN * TC_BM);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -336,8 +397,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[ab]);   // the accumulator may be reused
         const long long t0 = (long long)tile * kblocks;
-        p_first = tc_block_of_unit(t0, U, P);
-        p_last = tc_block_of_unit(t0 + kblocks - 1, U, P);
+        if (lead_share > 0) {
+          p_first = (tile - P) * lead_share;
+          p_last = p_first + lead_share - 1;
+        } else {
+          p_first = tc_block_of_unit(t0, U, P);
+          p_last = tc_block_of_unit(t0 + kblocks - 1, U, P);
+        }
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (et == 0) {
@@ -348,7 +414,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         write_out = last_s != 0;
         if (write_out) __threadfence();
       }
-      (void)u_seg;
       if (write_out) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -369,7 +434,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 const int qq = qb + i <= p_last ? qb + i : p_last;
-                const bool q_first = (int)(((long long)qq * U / P) / kblocks) == tile;
+                const bool q_first = lead_share == 0 && (int)(((long long)qq * U / P) / kblocks) == tile;
                 const float4* src = reinterpret_cast<const float4*>(
                     a.scratch + ((size_t)2 * qq + (q_first ? 0 : 1)) * (size_t)(BN * TC_BM) +
                     (size_t)r * BN + c0);
@@ -405,18 +470,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             float* pf = (float*)a.out + o0;
             bf16* pb = (bf16*)a.out + o0;
             const size_t ld = (size_t)a.ld;
-            const bool f32 = a.out_f32 != 0;
+            // No branch that only some lanes take: lanes 8-15 and 24-31 compute a value
+            // nobody stores, and the store is one predicated instruction.  A branch around
+            // the sixteen columns' work, taken by half of each warp, made a chunk of sixteen
+            // columns take 2.5 us (a plain chunk: 0.5 us).
+            if (a.out_f32) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float up = __shfl_down_sync(0xffffffffu, f[j], 8);
-              if (mine && j < valid) {
-                // bf16 output: the fast exponential and reciprocal are far inside its rounding
-                const float val = f[j] * __frcp_rn(1.0f + __expf(-f[j])) * up;
-                if (f32) *pf = val;
-                else *pb = __float2bfloat16_rn(val);
+              for (int j = 0; j < 16; ++j) {
+                const float up = __shfl_down_sync(0xffffffffu, f[j], 8);
+                const float val = __fdividef(f[j], 1.0f + __expf(-f[j])) * up;
+                st_f32_if(pf, val, mine && j < valid);
+                pf += ld;
               }
-              pf += ld;
-              pb += ld;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float up = __shfl_down_sync(0xffffffffu, f[j], 8);
+                // bf16 output: the fast exponential and division are far inside its rounding
+                const float val = __fdividef(f[j], 1.0f + __expf(-f[j])) * up;
+                st_bf16_if(pb, __float2bfloat16_rn(val), mine && j < valid);
+                pb += ld;
+              }
             }
           } else if (a.transpose_out) {
             // out[col_b][row_a]: lanes hold consecutive row_a, so each j is a coalesced store
@@ -509,6 +583,7 @@ static int pick_bn(int rowsB) {
 
 struct TcPlan {
   int bn, blocks, scratch_floats, counters;
+  int lead_share;   // > 0: the leftover deal with that many shares per leftover tile
 };
 
 // How many ways K is cut when the consumer adds the partials (split_k mode): as
@@ -542,14 +617,28 @@ static int tc_plan(int rowsA, int rowsB, int K, TcPlan* pl) {
   // that may share a tile is capped.
   const long long share = bn <= 16 ? TC_SHARE_16 : (bn <= 32 ? TC_SHARE_32 : TC_SHARE_64);
   if (blocks > tiles * share) blocks = tiles * share;
-  // With a few more tiles than SMs, a number of blocks that divides the tiles gives
-  // every block whole tiles and no tile is shared (152 tiles: 76 blocks of two).  For wide
-  // tiles, whose shared-tile hand-over is long, that is faster (batch 64: 9.2 k against
-  // 8.95 k tok/s); for narrow ones half the SMs stream too slowly (the gate|up product of a
-  // batch of 8 takes 28 us on 76 blocks against 21 us on 148: an SM draws about 47 GB/s).
-  if (tiles > sms && bn >= 64) {
+  // With more tiles than SMs but fewer than one and a half each (152 tiles on 148 SMs:
+  // the gate|up product of a decode step), the leftover deal: one whole tile per block and
+  // the rest cut over K and taken first.  Measured on that product, in a graph, against
+  // the even split of the line above: 18.4 against 21.6 us with 8 activation rows (ten
+  // shares), 28.8 against 30.0 us with 64 (four shares; there the even split had already
+  // lost to 76 blocks of two whole tiles, which an SM's draw of about 47 GB/s holds back).
+  // Failing that, for wide tiles, a number of blocks that divides the tiles, so that no
+  // tile is shared.
+  pl->lead_share = 0;
+  if (tiles > sms) {
+    const int kblocks = (K + TC_BK - 1) / TC_BK;
+    long long s = sms / (tiles - sms);   // as many shares as there are blocks to take them,
+    if (s > kblocks / 4) s = kblocks / 4;   // at least four k-blocks each,
+    const int most = bn <= 16 ? TC_LEAD_SHARE_16 : (bn <= 32 ? TC_LEAD_SHARE_32 : TC_LEAD_SHARE_64);
+    if (s > most) s = most;   // and not more than the adding block reads in passing
     const long long per = (tiles + sms - 1) / sms;
-    if (tiles % per == 0 && tiles / per >= sms / 2) blocks = tiles / per;
+    if (tiles < 2 * (long long)sms && s >= 2) {
+      blocks = sms;
+      pl->lead_share = (int)s;
+    } else if (bn >= 64 && tiles % per == 0 && tiles / per >= sms / 2) {
+      blocks = tiles / per;
+    }
   }
   pl->bn = bn;
   pl->blocks = (int)blocks;
@@ -560,7 +649,7 @@ static int tc_plan(int rowsA, int rowsB, int K, TcPlan* pl) {
 
 template <int BN>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, int blocks,
-                  cudaStream_t s) {
+                  int lead_share, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -568,7 +657,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a,
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return gb_launch(gemm_tc_kernel<BN>, dim3(blocks), dim3(TC_THREADS), TcConfig<BN>::SMEM, s, ma, mb, a);
+  return gb_launch(gemm_tc_kernel<BN>, dim3(blocks), dim3(TC_THREADS), TcConfig<BN>::SMEM, s, ma, mb, a, lead_share);
 }
 
 static int check_shape(int rowsA, int rowsB, int K) {
@@ -612,6 +701,7 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
     const int tiles = ((args->rowsA + TC_BM - 1) / TC_BM) * ((args->rowsB + pl.bn - 1) / pl.bn);
     if (args->split_k > (args->K + TC_BK - 1) / TC_BK) return GB_ERR_BAD_ARG;
     pl.blocks = tiles * args->split_k;
+    pl.lead_share = 0;
   }
   CUtensorMap ma, mb;
   e = make_map(&ma, A, args->rowsA, args->K, TC_BM);
@@ -619,11 +709,11 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   e = make_map(&mb, B, args->rowsB, args->K, pl.bn);
   if (e) return e;
   switch (pl.bn) {
-    case 16: return launch<16>(ma, mb, *args, pl.blocks, s);
-    case 32: return launch<32>(ma, mb, *args, pl.blocks, s);
-    case 64: return launch<64>(ma, mb, *args, pl.blocks, s);
-    case 128: return launch<128>(ma, mb, *args, pl.blocks, s);
-    case 256: return launch<256>(ma, mb, *args, pl.blocks, s);
+    case 16: return launch<16>(ma, mb, *args, pl.blocks, pl.lead_share, s);
+    case 32: return launch<32>(ma, mb, *args, pl.blocks, pl.lead_share, s);
+    case 64: return launch<64>(ma, mb, *args, pl.blocks, pl.lead_share, s);
+    case 128: return launch<128>(ma, mb, *args, pl.blocks, pl.lead_share, s);
+    case 256: return launch<256>(ma, mb, *args, pl.blocks, pl.lead_share, s);
   }
   return GB_ERR_UNSUPPORTED;
 }

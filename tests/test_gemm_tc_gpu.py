@@ -37,7 +37,10 @@ def test_prefill_orientation(M, N, K, out_dtype):
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 2560, 9728), (16, 6144, 2560), (33, 200, 264),
-                                   (64, 2560, 4096), (5, 19456, 2560)])
+                                   (64, 2560, 4096), (5, 19456, 2560),
+                                   # a few more tiles than SMs, wide tiles: the tiles beyond one
+                                   # per block are cut over K and taken first
+                                   (64, 19456, 2560), (40, 20000, 520), (100, 21000, 1032)])
 def test_decode_orientation(M, N, K, out_dtype):
     _check(M, N, K, out_dtype, swap=True)
 
@@ -54,6 +57,13 @@ def test_twice_in_a_row_and_row_independence():
     ops.check_kernel_errors()
     assert torch.equal(a, b)
     assert torch.equal(a[9:10], one)
+    # the same with leftover tiles shared out before every block's own tile
+    x, w = _rand((48, 520), 62).to(DEV), _rand((20000, 520), 63, 0.05).to(DEV)
+    a = ops.gemm_tc_bf16(x, w, torch.float32, swap=True)
+    b = ops.gemm_tc_bf16(x, w, torch.float32, swap=True)
+    torch.cuda.synchronize()
+    ops.check_kernel_errors()
+    assert torch.equal(a, b)
 
 
 @pytest.mark.parametrize("M", [1, 8, 33, 64])
