@@ -103,7 +103,10 @@ __global__ void qk_prepare_kernel(const QkPrepareArgs a) {
 template <typename WT, int P>
 __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
   pdl_launch_dependents_if_small();
-  pdl_wait();
+  // Positions, slots, the block table, the frequencies and the norm weights were in memory
+  // before the step began; only the product is the kernel before this one's.  So the
+  // position's sines, the page of its key and value and the weights are fetched before the
+  // wait for that kernel, and after it only the product's values remain on the path.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const int n_heads = a.nq + 2 * a.nkv;
@@ -125,6 +128,27 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
       }
     }
   }
+  size_t page_row0 = 0;   // row of (page of pos, kv head 0, pos in page)
+  bool paged = false;
+  if (a.k_pages) {
+    const int slot = a.slots[a.token_seq[t]];
+    if (slot >= 0) {
+      page_row0 = paged_row(a.block_table + (size_t)slot * a.max_pages, pos, 0, a.nkv, a.page, D);
+      paged = true;
+    }
+  }
+  float wq[NP][4], wk[NP][4];   // the norm weights of this lane's elements, for queries and keys
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    const int j = 2 * lane + 64 * p;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = (e < 2 ? j : HALF + j) + (e & 1);
+      wq[p][e] = (j < HALF && a.q_w) ? to_f32<WT>(((const WT*)a.q_w)[idx]) : 1.f;
+      wk[p][e] = (j < HALF && a.k_w) ? to_f32<WT>(((const WT*)a.k_w)[idx]) : 1.f;
+    }
+  }
+  pdl_wait();
   // heads of this token in turn: few blocks per token when there are many tokens
   for (int head = blockIdx.y * warps + warp; head < n_heads; head += gridDim.y * warps) {
     const bf16* src = (const bf16*)a.qkv + ((size_t)t * n_heads + head) * D;
@@ -163,8 +187,8 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
         lo[p][0] = lo[p][1] = hi[p][0] = hi[p][1] = 0.f;
       }
     }
-    const WT* w = kind == 0 ? (const WT*)a.q_w : (kind == 1 ? (const WT*)a.k_w : nullptr);
-    if (w) {
+    const bool normed = kind == 0 ? a.q_w != nullptr : (kind == 1 && a.k_w != nullptr);
+    if (normed) {
       float ss = 0.f;
 #pragma unroll
       for (int p = 0; p < NP; ++p)
@@ -173,13 +197,11 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
       const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
 #pragma unroll
       for (int p = 0; p < NP; ++p) {
-        const int j = 2 * lane + 64 * p;
-        if (j < HALF) {
-          lo[p][0] = lo[p][0] * inv * to_f32<WT>(w[j]);
-          lo[p][1] = lo[p][1] * inv * to_f32<WT>(w[j + 1]);
-          hi[p][0] = hi[p][0] * inv * to_f32<WT>(w[HALF + j]);
-          hi[p][1] = hi[p][1] * inv * to_f32<WT>(w[HALF + j + 1]);
-        }
+        // (beyond the head the values are zero and stay zero)
+        lo[p][0] = lo[p][0] * inv * (kind == 0 ? wq[p][0] : wk[p][0]);
+        lo[p][1] = lo[p][1] * inv * (kind == 0 ? wq[p][1] : wk[p][1]);
+        hi[p][0] = hi[p][0] * inv * (kind == 0 ? wq[p][2] : wk[p][2]);
+        hi[p][1] = hi[p][1] * inv * (kind == 0 ? wq[p][3] : wk[p][3]);
       }
     }
     if (kind != 2 && a.inv_freq) {
@@ -201,13 +223,8 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
       const int hh = kind == 1 ? head - a.nq : head - a.nq - a.nkv;
       if (a.kv_out)
         dst2 = (bf16*)a.kv_out + ((size_t)t * 2 * a.nkv + (kind == 1 ? hh : a.nkv + hh)) * D;
-      if (a.k_pages) {
-        const int slot = a.slots[a.token_seq[t]];
-        if (slot >= 0) {
-          const int* table = a.block_table + (size_t)slot * a.max_pages;
-          dst = (bf16*)(kind == 1 ? a.k_pages : a.v_pages) + paged_row(table, pos, hh, a.nkv, a.page, D);
-        }
-      }
+      if (paged)
+        dst = (bf16*)(kind == 1 ? a.k_pages : a.v_pages) + page_row0 + (size_t)hh * a.page * D;
     }
 #pragma unroll
     for (int p = 0; p < NP; ++p) {
