@@ -193,11 +193,21 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
       } else {
         const size_t p = ((size_t)seq * a.nq + h0 + row) * a.n_splits + split;
         a.part_o[p * D + d] = O;
-        if (d == 0) {
-          a.part_ml[p * 2] = M;
-          a.part_ml[p * 2 + 1] = L;
-        }
       }
+    }
+    // the rows' maxima and sums: one thread a row, after the loop (a branch for d == 0
+    // inside it would be entered by one lane alone in every other pass)
+    if (!single && tid < G) {
+      float M = -INFINITY, L = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < DC_WARPS; ++wi) M = fmaxf(M, red_m[wi * 16 + tid]);
+#pragma unroll
+      for (int wi = 0; wi < DC_WARPS; ++wi) {
+        const float mw = red_m[wi * 16 + tid];
+        L += red_l[wi * 16 + tid] * ((mw == -INFINITY) ? 0.f : exp2f(mw - M));
+      }
+      const size_t p = ((size_t)seq * a.nq + h0 + tid) * a.n_splits + split;
+      *reinterpret_cast<float2*>(a.part_ml + p * 2) = make_float2(M, L);
     }
   }
 }

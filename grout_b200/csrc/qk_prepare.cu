@@ -252,8 +252,9 @@ __global__ void qk_prepare_fast_kernel(const QkPrepareArgs a) {
 // head is D / 16 lanes and a warp prepares 32 / (D / 16) heads at a time; norm
 // weights and the token's rotation are fetched once and reused for every head.
 template <typename WT, int P>
-__global__ void qk_prepare_wide_kernel(const QkPrepareArgs a) {
-  pdl_wait();
+__global__ void __launch_bounds__(128, 8) qk_prepare_wide_kernel(const QkPrepareArgs a) {
+  // (what does not come from the kernel before this one, the product, is fetched
+  // before the wait for it, as in the kernel above)
   constexpr int D = 64 * P, HALF = D / 2, LPH = D / 16, HPW = 32 / LPH;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPH, j0 = 8 * (lane % LPH);
@@ -263,37 +264,52 @@ __global__ void qk_prepare_wide_kernel(const QkPrepareArgs a) {
   const int pos = a.token_pos[t];
   // the token's rotation: each angle is computed by one thread of the block and
   // shared (an accurate sine and cosine cost some forty instructions)
-  __shared__ float sn_s[HALF], cs_s[HALF];
+  // (and so are the norm weights: in registers they would cost the blocks per SM that keep
+  // enough loads in flight)
+  __shared__ __align__(16) float sn_s[HALF], cs_s[HALF], wq_s[D], wk_s[D];
   for (int j = threadIdx.x; j < HALF; j += blockDim.x) {
     float sj = 0.f, cj = 1.f;
     if (a.inv_freq) sincosf((float)pos * a.inv_freq[j], &sj, &cj);
     sn_s[j] = sj, cs_s[j] = cj;
   }
+  for (int j = threadIdx.x; j < D; j += blockDim.x) {
+    wq_s[j] = a.q_w ? to_f32<WT>(((const WT*)a.q_w)[j]) : 1.f;
+    wk_s[j] = a.k_w ? to_f32<WT>(((const WT*)a.k_w)[j]) : 1.f;
+  }
   __syncthreads();
-  float sn[8], cs[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) sn[e] = sn_s[j0 + e], cs[e] = cs_s[j0 + e];
-  float wq[16], wk[16];   // norm weights of this lane's elements: lo half, then hi half
-#pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    wq[e] = a.q_w ? to_f32<WT>(((const WT*)a.q_w)[j0 + e]) : 1.f;
-    wq[8 + e] = a.q_w ? to_f32<WT>(((const WT*)a.q_w)[HALF + j0 + e]) : 1.f;
-    wk[e] = a.k_w ? to_f32<WT>(((const WT*)a.k_w)[j0 + e]) : 1.f;
-    wk[8 + e] = a.k_w ? to_f32<WT>(((const WT*)a.k_w)[HALF + j0 + e]) : 1.f;
-  }
-  int slot = -1;
-  const int* table = nullptr;
+  size_t page_row0 = 0;   // row of (page of pos, kv head 0, pos in page)
+  bool paged = false;
   if (a.k_pages) {
-    slot = a.slots[a.token_seq[t]];
-    if (slot >= 0) table = a.block_table + (size_t)slot * a.max_pages;
+    const int slot = a.slots[a.token_seq[t]];
+    if (slot >= 0) {
+      page_row0 = paged_row(a.block_table + (size_t)slot * a.max_pages, pos, 0, a.nkv, a.page, D);
+      paged = true;
+    }
   }
+  pdl_wait();
   const int passes = (n_heads + HPW - 1) / HPW;
-  for (int pass = blockIdx.y * warps + warp; pass < passes; pass += gridDim.y * warps) {
+  // A warp's passes in groups of WIDE_U: the loads of a group are all requested before the
+  // first of them is used.  One pass at a time left 32 bytes a lane in flight and the
+  // kernel at half of the memory's rate.
+  constexpr int WIDE_U = 3;
+  const int stride = gridDim.y * warps;
+  for (int pass0 = blockIdx.y * warps + warp; pass0 < passes; pass0 += WIDE_U * stride) {
+  uint4 lo4s[WIDE_U], hi4s[WIDE_U];
+#pragma unroll
+  for (int u = 0; u < WIDE_U; ++u) {
+    const int head = (pass0 + u * stride) * HPW + sub;
+    const bool live = pass0 + u * stride < passes && head < n_heads;
+    const bf16* src = (const bf16*)a.qkv + ((size_t)t * n_heads + (live ? head : 0)) * D;
+    lo4s[u] = *reinterpret_cast<const uint4*>(src + j0);
+    hi4s[u] = *reinterpret_cast<const uint4*>(src + HALF + j0);
+  }
+#pragma unroll
+  for (int u = 0; u < WIDE_U; ++u) {
+    const int pass = pass0 + u * stride;
+    if (pass >= passes) break;            // the same for every lane of the warp
     const int head = pass * HPW + sub;
     const bool live = head < n_heads;     // every lane walks the loop: the sums below are warp-wide
-    const bf16* src = (const bf16*)a.qkv + ((size_t)t * n_heads + (live ? head : 0)) * D;
-    const uint4 lo4 = *reinterpret_cast<const uint4*>(src + j0);
-    const uint4 hi4 = *reinterpret_cast<const uint4*>(src + HALF + j0);
+    const uint4 lo4 = lo4s[u], hi4 = hi4s[u];
     float lo[8], hi[8];
     {
       const uint32_t lw[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, hw[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
@@ -314,18 +330,19 @@ __global__ void qk_prepare_wide_kernel(const QkPrepareArgs a) {
     for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (normed) {
       const float inv = 1.0f / sqrtf(ss / (float)D + a.eps);
+      const float* wn = kind == 0 ? wq_s : wk_s;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        lo[e] = lo[e] * inv * (kind == 0 ? wq[e] : wk[e]);
-        hi[e] = hi[e] * inv * (kind == 0 ? wq[8 + e] : wk[8 + e]);
+        lo[e] = lo[e] * inv * wn[j0 + e];
+        hi[e] = hi[e] * inv * wn[HALF + j0 + e];
       }
     }
     if (kind != 2 && a.inv_freq) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        const float l = lo[e], h = hi[e];
-        lo[e] = l * cs[e] - h * sn[e];
-        hi[e] = h * cs[e] + l * sn[e];
+        const float l = lo[e], h = hi[e], c = cs_s[j0 + e], sj = sn_s[j0 + e];
+        lo[e] = l * c - h * sj;
+        hi[e] = h * c + l * sj;
       }
     }
     uint4 lo_o, hi_o;
@@ -350,8 +367,8 @@ __global__ void qk_prepare_wide_kernel(const QkPrepareArgs a) {
       const int hh = kind == 1 ? head - a.nq : head - a.nq - a.nkv;
       if (a.kv_out)
         dst2 = (bf16*)a.kv_out + ((size_t)t * 2 * a.nkv + (kind == 1 ? hh : a.nkv + hh)) * D;
-      if (table)
-        dst = (bf16*)(kind == 1 ? a.k_pages : a.v_pages) + paged_row(table, pos, hh, a.nkv, a.page, D);
+      if (paged)
+        dst = (bf16*)(kind == 1 ? a.k_pages : a.v_pages) + page_row0 + (size_t)hh * a.page * D;
     }
     if (dst) {
       *reinterpret_cast<uint4*>(dst + j0) = lo_o;
@@ -361,6 +378,7 @@ __global__ void qk_prepare_wide_kernel(const QkPrepareArgs a) {
       *reinterpret_cast<uint4*>(dst2 + j0) = lo_o;
       *reinterpret_cast<uint4*>(dst2 + HALF + j0) = hi_o;
     }
+  }
   }
   pdl_launch_dependents();
 }
