@@ -571,3 +571,77 @@ def test_qk_prepare_takes_partial_sums(nq, nkv, D):
         pg = int(pc.table[pc.slot_of[s], p // 64])
         assert torch.allclose(kp[pg, :, p % 64].cpu().double(), want_k[r], **tol)
         assert torch.allclose(vp[pg, :, p % 64].cpu().double(), x[r, nq + nkv:], **tol)
+
+
+def test_pages_beyond_two_to_the_31_elements():
+    """The same sequences in the first pages of a cache and in pages whose element
+    offsets need more than 31 bits: every attention kernel and the q/k preparation
+    must return and store the same bits."""
+    ops = _ops()
+    dt = torch.bfloat16
+    nq, nkv, D, page = 16, 8, 128, 64
+    free, total = torch.cuda.mem_get_info()
+    far = (1 << 31) // (nkv * page * D) + 200           # first far page: offset > 2^31 elements
+    plan = [(0, 130), (70, 100), (0, 1), (5, 63)]
+    lens = [s + n for s, n in plan]
+    pc = Paged(lens, nkv, D, dt, 90, fill=0.0)
+    n_small = pc.k_pages.shape[0]
+    need = 2 * (far + n_small) * nkv * page * D * 2
+    if free < need + (2 << 30):
+        pytest.skip("not enough free device memory for a cache of 2^31 elements")
+    big_k = torch.empty((far + n_small, nkv, page, D), dtype=dt, device=DEV)
+    big_v = torch.empty_like(big_k)
+    big_k[far:] = pc.k_pages.to(DEV)
+    big_v[far:] = pc.v_pages.to(DEV)
+    big_k[:n_small].zero_()
+    big_v[:n_small].zero_()
+    near = (pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV))
+    there = (big_k, big_v, (pc.table + far).to(DEV))
+    q_lens = [n for _, n in plan]
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    q = _rand((T, nq, D), dt, 91).to(DEV)
+    qd = _rand((len(lens), nq, D), dt, 92).to(DEV)
+    scale = 1.0 / math.sqrt(D)
+    slots = torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV)
+    kvl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=DEV)
+    tok_seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(q_lens)]).to(DEV)
+    tok_pos = torch.cat([torch.arange(s, s + n, dtype=torch.int32) for s, n in plan]).to(DEV)
+
+    def all_kernels(kp, vp, table):
+        outs = [
+            ops.attn_decode_bf16(qd, kp, vp, table, slots=slots, kv_len=kvl, page=page, scale=scale,
+                                 max_kv_len=256, n_splits=3),
+            ops.attn_prefill_tc(q, kp, vp, table, cu_q=cu_t, slots=slots, kv_len=kvl,
+                                q_lens=tuple(q_lens), page=page, scale=scale),
+            ops.attn_prefill_bf16(q, kp, vp, table, cu_q=cu_t, slots=slots, kv_len=kvl,
+                                  q_lens=tuple(q_lens), page=page, scale=scale),
+            ops.attn_generic(q, kp, vp, table, token_seq=tok_seq, token_pos=tok_pos, slots=slots,
+                             page=page, scale=scale),
+        ]
+        torch.cuda.synchronize()
+        ops.check_kernel_errors()
+        return [o.clone() for o in outs]
+
+    a, b = all_kernels(*near), all_kernels(*there)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    # the q/k preparation stores the step's keys and values where the table says
+    qkv = _rand((T, (nq + 2 * nkv) * D), dt, 93).to(DEV)
+    w = _rand((D,), dt, 94).abs().to(DEV)
+    inv = (1.0 / (1e4 ** (torch.arange(0, D, 2).float() / D))).to(DEV)
+    near_kv = (near[0].clone(), near[1].clone())
+    for rows in (slice(cu[3], cu[4]), slice(0, T)):      # the few-token kernel, and a prompt's
+        stored = []
+        for (kp, vp, table), first in (((*near_kv, near[2]), 0), (there, far)):
+            ops.qk_prepare(qkv[rows], nq, nkv, D, q_w=w, k_w=w, eps=1e-6, inv_freq=inv, rot_dim=D,
+                           token_seq=tok_seq[rows], token_pos=tok_pos[rows], slots=slots,
+                           block_table=table, k_pages=kp, v_pages=vp, page=page)
+            torch.cuda.synchronize()
+            stored.append((kp[first:].clone(), vp[first:].clone()))
+        assert torch.equal(stored[0][0], stored[1][0]) and torch.equal(stored[0][1], stored[1][1])
+        assert not torch.equal(stored[0][0], near[0])        # something was stored
+    assert bool((big_k[:n_small] == 0).all()) and bool((big_v[:n_small] == 0).all())   # nothing strayed
