@@ -194,17 +194,18 @@ __global__ void add_rmsnorm_cluster_kernel(const float* res_in, const T* delta, 
     float a[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};
     if (res_in) Vec4<float>::load(res_in + s * N + i, a);
     if (delta) Vec4<T>::load(delta + s * N + i, d);
-    // four partials are requested at once and then added in order: one at a time, each
-    // load would wait for the one before it to have been added (a round trip to L2 each)
-    for (int k0 = 0; k0 < n_parts; k0 += 4) {
-      float pk[4][4];
+    // eight partials are requested at once and then added in order: one at a time, each
+    // load would wait for the one before it to have been added (a round trip to L2 each;
+    // a product is split at most eight ways, so this is one trip)
+    for (int k0 = 0; k0 < n_parts; k0 += 8) {
+      float pk[8][4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const int k = k0 + u < n_parts ? k0 + u : n_parts - 1;
         Vec4<float>::load(parts + (size_t)k * part_stride + s * N + i, pk[u]);
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < 8; ++u)
         if (k0 + u < n_parts) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) d[e] += pk[u][e];
