@@ -36,8 +36,19 @@
 // for its copies in flight, frees its tensor memory and returns.
 #include "tc_common.cuh"
 
-#ifndef TC_SMALL_STAGES
-#define TC_SMALL_STAGES 8
+// Stages of the ring for tiles of 16, 32 and 64 activation rows.  Six, not as many as
+// shared memory holds: with six (109 KB at 16 rows) two blocks fit on an SM, and the blocks
+// of the next product start requesting weights while this product's blocks are still in
+// their epilogues.  Measured on the whole decode step at batch 8: 8 stages 2.87 ms, 7: 2.86,
+// 6: 2.77, 5: 2.83; at batch 64 (one block per SM either way) six is the best too.
+#ifndef TC_STAGES_16
+#define TC_STAGES_16 6
+#endif
+#ifndef TC_STAGES_32
+#define TC_STAGES_32 6
+#endif
+#ifndef TC_STAGES_64
+#define TC_STAGES_64 6
 #endif
 #ifndef TC_SHARE_16
 #define TC_SHARE_16 6
@@ -115,10 +126,9 @@ struct TcConfig {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // both multiples of 1024
-  // As deep a ring as shared memory allows.  (Halving it so that the next product's
-  // block fits beside this one and streams during its fixup tail was measured: the
-  // shallower ring cost more than the overlap gained.)
-  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : TC_SMALL_STAGES);
+  // (wide tiles: as deep a ring as shared memory allows; narrow ones: see TC_STAGES_16)
+  static constexpr int STAGES =
+      BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? TC_STAGES_64 : (BN >= 32 ? TC_STAGES_32 : TC_STAGES_16)));
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256;
   // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
