@@ -233,6 +233,7 @@ def main() -> int:
         e2e = {"value": round(e2e_tps, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": 4 * args.batch}
 
+    eng.check()      # a kernel that gave up on a bounded wait would have voided the numbers
     print(json.dumps({
         "metric": f"decode tok/s (Qwen3-4B shape, batch {args.batch}, 2,048-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,

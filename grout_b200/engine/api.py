@@ -134,6 +134,15 @@ class Engine:
         probe = Model(plan, BuildContext(torch.bfloat16, torch.device("cpu")))
         return cls._build(arch, cfg, _Made(probe.expected()), dtype, device, **kw)
 
+    def check(self) -> None:
+        """Waits for the device and raises ``KernelError`` if a kernel gave up on one of
+        its bounded waits since the last check (its results are then void).  Generation
+        checks after every batch; a caller that steps by itself calls this where it
+        reads results."""
+        from ..kernels import ops
+        torch.cuda.synchronize(self.device)
+        ops.check_kernel_errors()
+
     # -- sequences -------------------------------------------------------------
     def open_sequence(self) -> int:
         return self.cache.open()
@@ -295,6 +304,6 @@ class Engine:
         ahead = self.choose_ahead if (look_ahead and device_argmax) else None
         loop = GenerationLoop(self, choose, max_batch=self.max_batch,
                               max_tokens=self.cache.max_tokens, max_seq_len=self.max_seq_len,
-                              vocab_size=self.vocab_size, sync=torch.cuda.synchronize,
+                              vocab_size=self.vocab_size, sync=self.check,
                               choose_ahead=ahead)
         return loop.run(requests)

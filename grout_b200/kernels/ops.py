@@ -415,7 +415,11 @@ _TC_ERROR_NAMES = {111: "a role of the tcgen05 attention kernel waited 2 s on a 
                    101: "the MMA warp waited 2 s for a stage that never arrived",
                    102: "the TMA producer waited 2 s for a stage that was never released",
                    103: "the epilogue waited 2 s for an accumulator that was never finished",
-                   104: "the MMA warp waited 2 s for an accumulator that was never drained"}
+                   104: "the MMA warp waited 2 s for an accumulator that was never drained",
+                   121: "the pair product's MMA lane waited 2 s for a stage that never arrived",
+                   122: "the pair product's producer waited 2 s for a stage that was never released",
+                   123: "the pair product's epilogue waited 2 s for an accumulator that was never finished",
+                   124: "the pair product's MMA lane waited 2 s for an accumulator that was never drained"}
 
 
 def _tc_error_flag(device) -> torch.Tensor:

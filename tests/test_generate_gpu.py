@@ -134,6 +134,24 @@ def test_limits(model_dirs):
         eng.step([(eng.open_sequence(), [256])])
 
 
+def test_a_kernel_that_gave_up_on_a_wait_is_reported(model_dirs):
+    """The tensor-memory kernels bound their waits and record a code in a device flag when
+    one runs out.  Generation reads the flag after every batch and raises; here the flag is
+    set by hand (no kernel is made to wait), and the next call is clean again."""
+    from grout_b200.engine import Engine
+    from grout_b200.kernels import ops
+    eng = Engine.load(model_dirs["A"], dtype="bfloat16", max_tokens=1024, max_batch=4, max_seq_len=128)
+    prompts = [random_tokens(9, TINY["A"]["vocab_size"], 77)]
+    good = eng.generate(prompts, max_new_tokens=4, ignore_eos=True)
+    ops._tc_error_flag(torch.device("cuda:0")).fill_(101)
+    with pytest.raises(ops.KernelError, match="stage that never arrived"):
+        eng.generate(prompts, max_new_tokens=4, ignore_eos=True)
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0                     # the batch's slots came back all the same
+    again = eng.generate(prompts, max_new_tokens=4, ignore_eos=True)
+    assert again[0].token_ids == good[0].token_ids
+
+
 def test_command_line(model_dirs, plain_weights, tmp_path):
     cfg, w = plain_weights["A"]
     prompt = random_tokens(9, 256, 780)
