@@ -89,29 +89,41 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
     // division sat in front of every tile's first copy)
     const int tpp_shift = (tiles_per_page & (tiles_per_page - 1)) == 0 ? __ffs(tiles_per_page) - 1 : -1;
 
-    auto load_tile = [&](int tile, int stage) {
-      const int pg = tpp_shift >= 0 ? tile >> tpp_shift : tile / tiles_per_page;
-      const int in_page = tile - pg * tiles_per_page;
-      const int page = table[pg];
-      const size_t base = (((size_t)page * a.nkv + kvh) * a.page + in_page * DC_BN) * D;
-      bf16* kd = my + (stage * 2 + 0) * DC_BN * LD;
-      bf16* vd = my + (stage * 2 + 1) * DC_BN * LD;
-      const int valid = kv_len - tile * DC_BN;
-      for (int i = lane; i < DC_BN * CHUNKS; i += 32) {
-        const int r = i / CHUNKS, ch = i % CHUNKS;
-        const bool ok = r < valid;
-        cp_async16(kd + r * LD + ch * 8, ok ? a.k_pages + base + r * D + ch * 8 : a.k_pages, ok);
-        cp_async16(vd + r * LD + ch * 8, ok ? a.v_pages + base + r * D + ch * 8 : a.v_pages, ok);
+    // Keys and values of a tile are copied, committed and waited for separately: the key
+    // buffer of a stage is refilled as soon as the scores of its tile are computed and the
+    // value buffer after the P.V product, so that with two buffers of each a tile and a half
+    // are in flight on average, not one.  Every thread commits the groups in the order
+    // K(0) V(0) K(1) V(1) ..., empty ones included, which is what the wait counts rely on.
+    auto load_half = [&](int tile, int stage, int which) {
+      if (tile < t_end) {
+        const int pg = tpp_shift >= 0 ? tile >> tpp_shift : tile / tiles_per_page;
+        const int in_page = tile - pg * tiles_per_page;
+        const int page = table[pg];
+        const size_t base = (((size_t)page * a.nkv + kvh) * a.page + in_page * DC_BN) * D;
+        bf16* dst = my + (stage * 2 + which) * DC_BN * LD;
+        const bf16* src = which ? a.v_pages : a.k_pages;
+        const int valid = kv_len - tile * DC_BN;
+        for (int i = lane; i < DC_BN * CHUNKS; i += 32) {
+          const int r = i / CHUNKS, ch = i % CHUNKS;
+          const bool ok = r < valid;
+          cp_async16(dst + r * LD + ch * 8, ok ? src + base + r * D + ch * 8 : src, ok);
+        }
       }
+      cp_async_commit();
     };
-    // the first tiles of this warp, then the producer, then the query tile
+    // the first tiles of this warp, then the producer, then the query tile.  A tile that
+    // holds the newest key comes last in its warp's list, so issuing what may be issued
+    // before the wait keeps the order of the groups.
     const int first = t_begin + warp;
-    bool early[DC_STAGES - 1];
+    bool early[DC_STAGES];
 #pragma unroll
-    for (int s = 0; s < DC_STAGES - 1; ++s) {
+    for (int s = 0; s < DC_STAGES; ++s) {
       const int tile = first + s * DC_WARPS;
-      early[s] = tile < t_end && tile != fresh_tile;
-      if (early[s]) load_tile(tile, s);
+      early[s] = tile >= t_end || tile != fresh_tile;
+      if (early[s]) {
+        load_half(tile, s, 0);
+        load_half(tile, s, 1);
+      }
     }
     pdl_wait();
     // the query tile: G rows, the rest zero
@@ -122,34 +134,44 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
         const bool ok = r < G;
         cp_async16(q_s + r * LD + ch * 8, ok ? qsrc + r * D + ch * 8 : qsrc, ok);
       }
+      cp_async_commit();   // a group of its own; everything so far is waited for before the loop
     }
     WarpAttn<DT> w;
     w.init();
     int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
 #pragma unroll
-    for (int s = 0; s < DC_STAGES - 1; ++s) {   // what had to wait for the producer
-      const int tile = first + s * DC_WARPS;
-      if (!early[s] && tile < t_end) load_tile(tile, s);
+    for (int s = 0; s < DC_STAGES; ++s) {   // what had to wait for the producer
+      if (!early[s]) {
+        load_half(first + s * DC_WARPS, s, 0);
+        load_half(first + s * DC_WARPS, s, 1);
+      }
     }
-    cp_async_commit();
     cp_async_wait<0>();   // the query tile and this warp's first tiles have landed for this thread
     __syncthreads();      // ... and for all threads
     w.load_q(q_s);
     int stage = 0;
+    // behind the keys of a tile in the order of the groups: its values and both halves of
+    // the DC_STAGES - 1 tiles after it; behind its values, once the next keys are issued: the same count
+    constexpr int BEHIND = 2 * DC_STAGES - 1;
     for (int tile = first; tile < t_end; tile += DC_WARPS, stage = stage + 1 == DC_STAGES ? 0 : stage + 1) {
-      const int ahead = tile + (DC_STAGES - 1) * DC_WARPS;
-      if (ahead < t_end) load_tile(ahead, stage == 0 ? DC_STAGES - 1 : stage - 1);
-      cp_async_commit();
-      cp_async_wait<DC_STAGES - 1>();
+      cp_async_wait<BEHIND>();
       __syncwarp();
       const int key0 = tile * DC_BN;
       const bf16* kt = my + (stage * 2 + 0) * DC_BN * LD;
       const bf16* vt = my + (stage * 2 + 1) * DC_BN * LD;
+      const int refill = tile + DC_STAGES * DC_WARPS;
+      auto between = [&] {
+        __syncwarp();   // all lanes have read the keys
+        load_half(refill, stage, 0);
+        cp_async_wait<BEHIND>();
+        __syncwarp();   // the values have landed for every lane
+      };
       if (key0 < key_lo || key0 + DC_BN - 1 > pos)
-        w.template tile<DC_BN, true>(kt, vt, key0, lo, hi, a.scale_log2);
+        w.template tile<DC_BN, true>(kt, vt, key0, lo, hi, a.scale_log2, between);
       else
-        w.template tile<DC_BN, false>(kt, vt, key0, lo, hi, a.scale_log2);
-      __syncwarp();  // all lanes are done with the stage before it is refilled
+        w.template tile<DC_BN, false>(kt, vt, key0, lo, hi, a.scale_log2, between);
+      __syncwarp();  // all lanes are done with the values before their buffer is refilled
+      load_half(refill, stage, 1);
     }
     cp_async_wait<0>();
     pdl_launch_dependents();   // the key stream of this block is over

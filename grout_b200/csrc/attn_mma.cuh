@@ -85,6 +85,15 @@ struct WarpAttn {
   template <int NKEYS, bool MASK>
   __device__ __forceinline__ void tile(const bf16* k_tile, const bf16* v_tile, int key0,
                                        const int (&lo)[2], const int (&hi)[2], float c) {
+    tile<NKEYS, MASK>(k_tile, v_tile, key0, lo, hi, c, [] {});
+  }
+
+  // The same with `between()` called once the scores are computed, that is when k_tile has
+  // been read for the last time and before v_tile is read for the first: a caller that
+  // pipelines its copies refills the key buffer and waits for the values there.
+  template <int NKEYS, bool MASK, typename F>
+  __device__ __forceinline__ void tile(const bf16* k_tile, const bf16* v_tile, int key0,
+                                       const int (&lo)[2], const int (&hi)[2], float c, F&& between) {
     const int lane = threadIdx.x & 31, t = lane & 3;
     constexpr int NT = NKEYS / 8;
     float s[NT][4];
@@ -106,6 +115,7 @@ struct WarpAttn {
         }
       }
     }
+    between();
     // scale into the log2 domain, mask, row maxima
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
