@@ -309,6 +309,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       bool first = true;
       int seg = 0;
       bool ok = true;
+      // both ranges in turn; the body keeps its indentation, it is one loop over segments
       for (int rg = 0; rg < 2; ++rg)
       for (long long u = rg ? rb1 : rb0, u_end = rg ? re1 : re0; u < u_end && ok; ++seg) {
         const int tile = (int)(u / kblocks);
@@ -358,6 +359,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int et = threadIdx.x - 64;      // 0..127 among the epilogue threads
     int seg = 0;
     bool ok = true;
+    // (both ranges in turn, as in the MMA lane)
     for (int rg = 0; rg < 2; ++rg)
     for (long long u = rg ? rb1 : rb0, u_end = rg ? re1 : re0; u < u_end && ok; ++seg) {
       const int tile = (int)(u / kblocks);
