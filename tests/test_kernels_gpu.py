@@ -427,7 +427,7 @@ def test_attn_prefill_bf16(nq, nkv, D, window):
         assert torch.allclose(got[cu[4] + 199, 0].double(), pc.v[4][3, 0].double(), atol=1e-2, rtol=1e-2)
 
 
-@pytest.mark.parametrize("n_splits", [1, 3, None])
+@pytest.mark.parametrize("n_splits", [1, 3, 11, None])     # 11: more partials than the merge requests at once
 @pytest.mark.parametrize("window", [None, 70])
 @pytest.mark.parametrize("nq,nkv,D", [(6, 2, 48), (8, 1, 128), (3, 3, 16), (32, 8, 128), (16, 1, 32)])
 def test_attn_decode_bf16(nq, nkv, D, window, n_splits):
@@ -456,6 +456,34 @@ def test_attn_decode_bf16(nq, nkv, D, window, n_splits):
     assert bool((got[B - 1] == 0).all())            # the padding row
     if window is None:
         assert torch.allclose(got[2, 0].double(), pc.v[2][5, 0].double(), atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("n_splits", [1, 2, 5])
+def test_attn_decode_many_tiles_per_warp(n_splits):
+    """Long sequences, so that each warp refills its key and value buffers many times (its
+    copies of keys and of values are committed and waited for separately).  One query looks
+    at a single far key, whose value must come back."""
+    dt = torch.bfloat16
+    nq, nkv, D = 8, 2, 128
+    lens = [1500, 700, 33]
+    pc = Paged(lens, nkv, D, dt, 48)
+    q = _rand((len(lens), nq, D), dt, 49)
+    scale = 1.0 / math.sqrt(D)
+    q[0] = 0
+    q[0, :, 0] = 30.0
+    pc.k[0][:, :, 0] = 0
+    pc.k[0][777, :, 0] = 30.0
+    for j in range(lens[0]):
+        pc.store(0, j, pc.k[0][j], pc.v[0][j])
+    got = _ops().attn_decode_bf16(
+        q.to(DEV), pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV),
+        slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
+        kv_len=torch.tensor(lens, dtype=torch.int32, device=DEV), page=64, scale=scale,
+        max_kv_len=1536, n_splits=n_splits).cpu()
+    for s, n in enumerate(lens):
+        want = _attn_oracle(q[s], pc.k[s], pc.v[s], n - 1, scale, None)
+        assert torch.allclose(got[s].double(), want, **FAST_TOL), (s, n)
+    assert torch.allclose(got[0, 0].double(), pc.v[0][777, 0].double(), atol=1e-2, rtol=1e-2)
 
 
 def test_fast_attention_refuses_what_it_cannot_do():
