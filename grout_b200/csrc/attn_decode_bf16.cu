@@ -49,8 +49,9 @@ __global__ void __launch_bounds__(DC_THREADS) attn_decode_kernel(const DecodeArg
   const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
   const int G = a.nq / a.nkv;
   const int h0 = kvh * G;
-  const int slot = a.slots[seq];
-  const int kv_len = slot < 0 ? 0 : a.kv_len[seq];
+  // (both loads at once: the length does not wait for the slot)
+  const int slot = a.slots[seq], len_seq = a.kv_len[seq];
+  const int kv_len = slot < 0 ? 0 : len_seq;
   const bool single = a.n_splits == 1;
 
   // key tiles of this split
