@@ -29,7 +29,9 @@ def apply_chat_template(prompt: str) -> str:
 
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="grout_b200", description="Qwen3 dense text generation on one B200")
-    ap.add_argument("--model", required=True, help="model folder (config.json, safetensors)")
+    ap.add_argument("--model", required=True,
+                    help="model folder (config.json, safetensors), or random:CONFIG.json for "
+                         "random weights made on the device from --seed (with --prompt-ids)")
     g = ap.add_mutually_exclusive_group(required=True)
     g.add_argument("--prompt", help="text; needs tokenizer.json in the model folder")
     g.add_argument("--prompt-ids", help="comma-separated token ids, bypassing the tokenizer")
@@ -49,6 +51,14 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--warmup-reps", type=int, default=1,
                     help="discarded generations before the measured one")
     ap.add_argument("--ignore-eos", action="store_true", help="generate the whole budget")
+    ap.add_argument("--reps", type=int, default=1,
+                    help="measured generations; each prints its times (grout_bench.rs:49-50)")
+    ap.add_argument("--json", default=None, metavar="FILE",
+                    help="append one JSON object per measured generation to FILE (JSON lines, "
+                         "the keys of grout_bench.rs:60-66)")
+    ap.add_argument("--variant", default="default", help="label of the `variant` field of --json")
+    ap.add_argument("--quiet", action="store_true",
+                    help="do not print the generated text or the profile, only the times")
     ap.add_argument("--fp32", action="store_true", help="run the true 32-bit path")
     ap.add_argument("--output-json", default=None, help="write token ids, counts and seconds here")
     ap.add_argument("--device", default="cuda:0")
@@ -62,6 +72,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     from .sampling import SamplingParams
 
     tokenizer = None
+    random_config = args.model[len("random:"):] if args.model.startswith("random:") else None
+    if random_config is not None and args.prompt is not None:
+        print("error: random weights have no tokenizer; use --prompt-ids", file=sys.stderr)
+        return 2
     if args.prompt is not None:
         path = os.path.join(args.model, "tokenizer.json")
         if not os.path.exists(path):
@@ -81,8 +95,14 @@ def main(argv: Optional[List[str]] = None) -> int:
             print("error: --prompt-ids takes comma-separated integers", file=sys.stderr)
             return 2
 
-    engine = Engine.load(args.model, dtype="float32" if args.fp32 else "bfloat16",
-                         device=args.device, max_seq_len=args.max_seq_len, max_batch=1)
+    dtype = "float32" if args.fp32 else "bfloat16"
+    if random_config is not None:
+        with open(random_config, encoding="utf-8") as fh:
+            engine = Engine.random(json.load(fh), args.seed, dtype=dtype, device=args.device,
+                                   max_seq_len=args.max_seq_len, max_batch=1)
+    else:
+        engine = Engine.load(args.model, dtype=dtype, device=args.device,
+                             max_seq_len=args.max_seq_len, max_batch=1)
     base = engine.default_sampling(args.sample, args.seed)
     sampling = SamplingParams(args.sample,
                               args.temperature if args.temperature is not None else base.temperature,
@@ -101,15 +121,32 @@ def main(argv: Optional[List[str]] = None) -> int:
         run(min(args.max_new_tokens, 8))
     if args.profile:
         engine.profile = StepProfile()
-    out = run(args.max_new_tokens)
+    reps = max(1, args.reps)
+    for i in range(reps):                      # benchmarks/src/bin/grout_bench.rs:96-110, 150-190
+        out = run(args.max_new_tokens)
+        if reps > 1 or args.json:
+            print(f"  run {i + 1}/{reps}: prompt_tokens={out.prompt_tokens}, "
+                  f"gen_tokens={out.generated_tokens}, prefill_ms={out.prompt_elapsed * 1e3:.2f}, "
+                  f"decode_ms={out.decode_elapsed * 1e3:.2f}, e2e_ms={out.total_elapsed * 1e3:.2f}, "
+                  f"decode_phase_tps={out.decode_phase_tps():.1f}, e2e_tps={out.total_tps():.1f}")
+        if args.json:
+            with open(args.json, "a", encoding="utf-8") as fh:
+                fh.write(json.dumps({"engine": "grout_b200", "variant": args.variant,
+                                     "pp": out.prompt_tokens, "tg": args.max_new_tokens, "rep": i,
+                                     "prompt_tokens": out.prompt_tokens,
+                                     "gen_tokens": out.generated_tokens,
+                                     "prefill_ms": out.prompt_elapsed * 1e3,
+                                     "decode_ms": out.decode_elapsed * 1e3,
+                                     "e2e_ms": out.total_elapsed * 1e3}) + "\n")
     text = tokenizer.decode(out.token_ids, skip_special_tokens=False) if tokenizer else None
-    print()
-    print(text if text is not None else " ".join(str(t) for t in out.token_ids))
+    if not args.quiet:
+        print()
+        print(text if text is not None else " ".join(str(t) for t in out.token_ids))
     print(f"t/s: {out.prompt_tps():.2f} prompt, {out.decode_phase_tps():.2f} decode phase, "
           f"{out.total_tps():.2f} end-to-end (prompt_tokens={out.prompt_tokens}, "
           f"generated_tokens={out.generated_tokens}, prompt_s={out.prompt_elapsed:.3f}, "
           f"decode_s={out.decode_elapsed:.3f}, total_s={out.total_elapsed:.3f})")
-    if args.profile:
+    if args.profile and not args.quiet:
         print()
         print(engine.profile.report())
     if args.output_json:

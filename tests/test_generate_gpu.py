@@ -168,3 +168,28 @@ def test_command_line(model_dirs, plain_weights, tmp_path):
         assert rec["token_ids"] == plain.greedy_generate(w, cfg, prompt, 6)
         assert rec["generated_tokens"] == 6 and rec["prompt_tokens"] == 9
     assert "profile:" in r.stdout
+    # the bench binary's options: several measured generations, one JSON line each
+    lines = str(tmp_path / "runs.jsonl")
+    r = subprocess.run([sys.executable, "-m", "grout_b200", "--model", model_dirs["A"],
+                        "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "5",
+                        "--ignore-eos", "--reps", "3", "--json", lines, "--variant", "t", "--quiet"],
+                       capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    recs = [json.loads(l) for l in open(lines)]
+    assert [x["rep"] for x in recs] == [0, 1, 2]
+    assert all(x["gen_tokens"] == 5 and x["prompt_tokens"] == 9 and x["variant"] == "t" and
+               x["e2e_ms"] >= x["decode_ms"] > 0 for x in recs)
+    assert "run 3/3" in r.stdout and "profile:" not in r.stdout
+    # random weights from a configuration file and a seed: the same seed, the same tokens
+    # (configuration B: its output head is not tied to the embedding, so that the greedy
+    # continuation is not just the last token again, whatever the weights)
+    seen = []
+    for seed in ("4", "4", "5"):
+        r = subprocess.run([sys.executable, "-m", "grout_b200", "--model",
+                            "random:" + os.path.join(model_dirs["B"], "config.json"), "--seed", seed,
+                            "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6",
+                            "--ignore-eos", "--output-json", out],
+                           capture_output=True, text=True, env=env, cwd=ROOT, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        seen.append(json.load(open(out))["token_ids"])
+    assert seen[0] == seen[1] and seen[0] != seen[2] and len(seen[0]) == 6
