@@ -605,6 +605,13 @@ static int tc_split(int rowsA, int rowsB, int K, int sms) {
   const long long tiles = (long long)((rowsA + TC_BM - 1) / TC_BM) * ((rowsB + bn - 1) / bn);
   const int kblocks = (K + TC_BK - 1) / TC_BK;
   long long s = sms / tiles;
+#ifndef TC_SPLIT_OVER
+#define TC_SPLIT_OVER 6
+#endif
+  // Two blocks of the narrowest tiles fit on an SM, so a few more blocks than SMs cost
+  // nothing, and one more cut fills the GPU where tiles * s falls well short of it
+  // (40 tiles: 160 blocks instead of 120 on 148 SMs).
+  if (bn <= 16 && TC_SPLIT_OVER > 0 && tiles * (s + 1) <= sms + sms / TC_SPLIT_OVER) s += 1;
   if (s > kblocks / 4) s = kblocks / 4;
   if (s > 8) s = 8;
   return s < 2 ? 0 : (int)s;   // 0: not worth it (the product already has enough tiles)
