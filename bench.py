@@ -30,6 +30,20 @@ QWEN3_4B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_si
                 rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=True,
                 use_sliding_window=False, eos_token_id=151645)
 FULL_LAYERS = 36
+# The other two model sizes of the workload list, for --requests (layer sizes only; the
+# default run and its contract stay with the 4B sizes).
+SIZES = {
+    "4b": QWEN3_4B,
+    "8b": dict(QWEN3_4B, hidden_size=4096, intermediate_size=12288, tie_word_embeddings=False),
+    "32b": dict(QWEN3_4B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64,
+                num_attention_heads=64, tie_word_embeddings=False),
+}
+# What the reference publishes for Qwen3-32B on a B200 (fp16, batch 1, its own engine):
+# request_gen_tps = generated tokens / seconds of the whole request, and one prefill time
+# (benchmarks/RESULTS.md:29-31, 45-47, 53-55).  (prompt tokens, generated tokens) -> figure.
+PUBLISHED_32B = {(18, 36): 79.6, (18, 128): 79.9, (18, 512): 80.1, (128, 36): 79.0, (512, 36): 75.3,
+                 (2048, 36): 61.4, (8192, 36): 37.2}
+PUBLISHED_32B_PREFILL_MS = {8192: 513.78}
 CONTEXT = 4096
 PROMPT = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -103,6 +117,46 @@ def prefill_flops(cfg, layers, T):
     return layers * (linear + attn) + 2 * V * H
 
 
+def run_requests(size: str, reps: int) -> int:
+    """The reference's own request grid (one sequence: prompt of P tokens, T tokens generated,
+    EOS ignored) through ``Engine.generate`` with random weights of the named size and random
+    token ids: generated tokens per second of the whole request, host tokens in and out; the
+    median of ``reps`` requests after two that are discarded, half a second apart."""
+    import torch
+    from grout_b200.engine import Engine
+    cfg = SIZES[size]
+    eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=8192 + 576, max_batch=1,
+                        max_seq_len=8192 + 512 + 64)
+    g = torch.Generator().manual_seed(1)
+
+    def prompt(n):
+        return torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
+
+    cells = []
+    for pp, tg in sorted(PUBLISHED_32B):
+        runs = []
+        for i in range(reps + 2):
+            time.sleep(0.5)
+            o = eng.generate([prompt(pp)], tg, ignore_eos=True)[0]
+            if i >= 2:
+                runs.append((o.generated_tokens / o.total_elapsed, o.prompt_elapsed * 1e3,
+                             o.decode_phase_tps()))
+        cell = {"prompt": pp, "generate": tg,
+                "request_gen_tps": round(statistics.median(r[0] for r in runs), 1),
+                "prefill_ms": round(statistics.median(r[1] for r in runs), 2),
+                "decode_phase_tps": round(statistics.median(r[2] for r in runs), 1)}
+        if size == "32b":
+            cell["published_request_gen_tps"] = PUBLISHED_32B[(pp, tg)]
+            if pp in PUBLISHED_32B_PREFILL_MS:
+                cell["published_prefill_ms"] = PUBLISHED_32B_PREFILL_MS[pp]
+        cells.append(cell)
+    eng.check()
+    print(json.dumps({"metric": f"request_gen_tps, one sequence, Qwen3-{size.upper()} layer sizes",
+                      "unit": "tok/s", "dtype": "bf16", "data": "synthetic", "reps": reps,
+                      "layers": cfg["num_hidden_layers"], "cells": cells}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -115,6 +169,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--phases", default="prefill,decode,points,e2e",
                     help="which measurements to run (a profiler wants one at a time)")
+    ap.add_argument("--requests", default=None, choices=sorted(SIZES),
+                    help="instead of the default run: the reference's request grid at this model size")
+    ap.add_argument("--reps", type=int, default=5, help="measured requests per cell of --requests")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -125,6 +182,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.requests:
+        return run_requests(args.requests, max(1, args.reps))
     W = max(args.warmup, 3)
     K = args.steps
     phases = set(args.phases.split(","))
