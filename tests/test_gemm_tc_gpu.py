@@ -30,7 +30,9 @@ def _check(M, N, K, out_dtype, swap, seed=0):
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (300, 200, 264), (2048, 512, 2560),
-                                   (70, 1000, 96), (513, 130, 4096)])
+                                   (70, 1000, 96), (513, 130, 4096),
+                                   # 160 and 190 tiles on 148 SMs: leftover tiles cut over K
+                                   (1280, 4096, 520), (1200, 4800, 1032)])
 def test_prefill_orientation(M, N, K, out_dtype):
     _check(M, N, K, out_dtype, swap=False)
 
