@@ -121,6 +121,41 @@ __device__ __forceinline__ int tc_block_of_unit(long long u, long long U, int P)
   return (int)(((u + 1) * P - 1) / U);
 }
 
+// The units [rb0, re0) and then [rb1, re1) of the line (tile-major, k-blocks within a tile)
+// that block p of P works, for the three ways of dealing: split_k > 0 (block p = tile * S + s
+// takes the s-th share of its tile's k-blocks), the leftover deal (lead_share > 0: tile p
+// whole, before it a share of one of the tiles beyond the P-th), else equal shares of the
+// line.  Host and device use the same function; a host-side test checks that the blocks of
+// a launch cover every unit exactly once.  Returns the share's index within its tile in a
+// split-K launch, else 0.
+__host__ __device__ inline int tc_ranges(int p, int P, int tiles, int kblocks, int split_k, int lead_share,
+                                         long long& rb0, long long& re0, long long& rb1, long long& re1) {
+  // (the shares of one tile are cut in 32-bit arithmetic: share * kblocks is far below 2^31,
+  // and a 64-bit division costs every thread of every block a hundred cycles at its start)
+  rb0 = re0 = 0;
+  if (split_k > 0) {
+    const int tile = p / split_k, sh = p - tile * split_k;
+    rb1 = (long long)tile * kblocks + sh * kblocks / split_k;
+    re1 = (long long)tile * kblocks + (sh + 1) * kblocks / split_k;
+    return sh;
+  }
+  if (lead_share > 0) {
+    rb1 = (long long)p * kblocks;
+    re1 = rb1 + kblocks;
+    const int n_left = tiles - P;
+    if (p < n_left * lead_share) {
+      const int j = p / lead_share, sh = p - j * lead_share;
+      rb0 = (long long)(P + j) * kblocks + sh * kblocks / lead_share;
+      re0 = (long long)(P + j) * kblocks + (sh + 1) * kblocks / lead_share;
+    }
+    return 0;
+  }
+  const long long U = (long long)tiles * kblocks;
+  rb1 = p * U / P;
+  re1 = (p + 1) * U / P;
+  return 0;
+}
+
 template <int BN>
 struct TcConfig {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
@@ -163,23 +198,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   // the units of this block: two ranges of the line, worked in this order (the first is
   // empty except in the leftover deal)
   // (scalars, not arrays: an array indexed by the range would live in local memory)
-  long long rb0 = 0, re0 = 0, rb1 = p * U / P, re1 = (p + 1) * U / P;
-  int split_index = 0;
-  if (a.split_k > 0) {   // block p = tile * S + s takes the s-th share of its tile's k-blocks
-    const int tile = p / a.split_k;
-    split_index = p - tile * a.split_k;
-    rb1 = (long long)tile * kblocks + (long long)split_index * kblocks / a.split_k;
-    re1 = (long long)tile * kblocks + (long long)(split_index + 1) * kblocks / a.split_k;
-  } else if (lead_share > 0) {
-    rb1 = (long long)p * kblocks;
-    re1 = rb1 + kblocks;
-    const int n_left = tiles_a * tiles_b - P;
-    if (p < n_left * lead_share) {
-      const int j = p / lead_share, sh = p - j * lead_share;
-      rb0 = (long long)(P + j) * kblocks + (long long)sh * kblocks / lead_share;
-      re0 = (long long)(P + j) * kblocks + (long long)(sh + 1) * kblocks / lead_share;
-    }
-  }
+  long long rb0, re0, rb1, re1;
+  // (split_index: which share of its tile's k-blocks, in a split-K launch)
+  const int split_index = tc_ranges(p, P, tiles_a * tiles_b, kblocks, a.split_k, lead_share, rb0, re0, rb1, re1);
 
   if (threadIdx.x == 0) {
     tma_prefetch_map(&map_a);
@@ -617,6 +638,7 @@ static int tc_split(int rowsA, int rowsB, int K, int sms) {
   return s < 2 ? 0 : (int)s;   // 0: not worth it (the product already has enough tiles)
 }
 
+static int tc_plan_for(int rowsA, int rowsB, int K, int sms, TcPlan* pl);
 static int tc_plan(int rowsA, int rowsB, int K, TcPlan* pl) {
   static int sms = 0;
   if (!sms) {
@@ -625,6 +647,10 @@ static int tc_plan(int rowsA, int rowsB, int K, TcPlan* pl) {
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return (int)e;
   }
+  return tc_plan_for(rowsA, rowsB, K, sms, pl);
+}
+// (the plan for a GPU of `sms` SMs: no device is asked, so a host-side test can call it)
+static int tc_plan_for(int rowsA, int rowsB, int K, int sms, TcPlan* pl) {
   const int bn = pick_bn(rowsB);
   const long long tiles = (long long)((rowsA + TC_BM - 1) / TC_BM) * ((rowsB + bn - 1) / bn);
   const long long units = tiles * ((K + TC_BK - 1) / TC_BK);
@@ -702,6 +728,28 @@ GB_EXPORT int gb_gemm_tc_plan(int rowsA, int rowsB, int K, int* plan) {
   plan[2] = pl.scratch_floats;
   plan[3] = pl.counters;
   plan[4] = tc_split(rowsA, rowsB, K, sms);
+  return 0;
+}
+
+// For host-side tests, no device needed.  plan[0..4] as above for a GPU of `sms` SMs, plan[5] =
+// shares of the leftover deal (0: none).
+GB_EXPORT int gb_gemm_tc_plan_for(int rowsA, int rowsB, int K, int sms, int* plan) {
+  int e = check_shape(rowsA, rowsB, K);
+  if (e) return e;
+  if (sms <= 0) return GB_ERR_BAD_ARG;
+  TcPlan pl;
+  e = tc_plan_for(rowsA, rowsB, K, sms, &pl);
+  if (e) return e;
+  plan[0] = pl.bn, plan[1] = pl.blocks, plan[2] = pl.scratch_floats, plan[3] = pl.counters;
+  plan[4] = tc_split(rowsA, rowsB, K, sms);
+  plan[5] = pl.lead_share;
+  return 0;
+}
+// ranges[0..3] = rb0, re0, rb1, re1 of block p of P (see tc_ranges).
+GB_EXPORT int gb_gemm_tc_ranges(int p, int P, int tiles, int kblocks, int split_k, int lead_share,
+                                long long* ranges) {
+  if (p < 0 || P <= 0 || p >= P || tiles <= 0 || kblocks <= 0) return GB_ERR_BAD_ARG;
+  tc_ranges(p, P, tiles, kblocks, split_k, lead_share, ranges[0], ranges[1], ranges[2], ranges[3]);
   return 0;
 }
 
