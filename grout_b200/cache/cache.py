@@ -17,7 +17,7 @@ from typing import Dict, List, Optional, Sequence, Tuple, Union
 import torch
 
 from .slots import SlotList
-from .spec import CacheFull, KVSpec, PAGE_TOKENS, StateSpec
+from .spec import CacheFull, KVSpec, StateSpec
 from .stores import KVStore, StateStore, pages_for
 
 

@@ -11,7 +11,6 @@ import argparse
 import json
 import os
 import sys
-import time
 from typing import List, Optional
 
 IM_START, IM_END = "<|im_start|>", "<|im_end|>"

@@ -16,7 +16,7 @@ import json
 import os
 import typing
 from dataclasses import dataclass, field, fields, MISSING
-from typing import Any, Optional, Union
+from typing import Any, Union
 
 
 class ConfigError(ValueError):

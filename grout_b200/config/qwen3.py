@@ -8,7 +8,7 @@ checkpoints derive are defaulted here the way its packed-model parser does
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Optional, Tuple, Union
+from typing import Optional, Tuple, Union
 
 from .base import ModelConfig
 

@@ -14,7 +14,6 @@ for one sequence, src/model.rs:2272-2308.)
 """
 from __future__ import annotations
 
-import os
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch

@@ -17,7 +17,7 @@ from typing import Dict
 import numpy as np
 import torch
 
-from .batch import context_from, layout_sizes, pack_step
+from .batch import context_from, layout_sizes
 
 
 def bucket_for(n: int, largest: int) -> int:

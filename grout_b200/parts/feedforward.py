@@ -7,7 +7,6 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
 from .base import BuildContext, ParamSpec, Part, register_part
 from .linear import Linear
 

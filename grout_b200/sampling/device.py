@@ -1,7 +1,7 @@
 """Choosing tokens on the GPU from the step's 32-bit logits."""
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import Sequence
 
 import numpy as np
 import torch

@@ -13,7 +13,7 @@ int32.  The true 32-bit path widens everything to float32.
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, Iterable, Tuple
+from typing import Callable, Dict, Tuple
 
 import torch
 
