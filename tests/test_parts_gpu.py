@@ -1,6 +1,5 @@
 """Each part alone: built from its spec, given random tensors, run on a small
 step, and compared with the plain implementation's function for that part."""
-import math
 
 import pytest
 import torch

@@ -4,7 +4,7 @@ import math
 import numpy as np
 import torch
 
-from conftest import TINY, random_tokens
+from conftest import random_tokens
 from plain import qwen3 as plain
 from plain import sampling as plain_sampling
 

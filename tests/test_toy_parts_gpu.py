@@ -2,8 +2,6 @@
 without a change to its files: a mixer with fixed-size state of its own, a layer
 that runs twice, and an attention layer that reads another layer's cache.
 The toy model is nobody's architecture; it only shows the interfaces."""
-import json
-import math
 import os
 from dataclasses import dataclass
 
@@ -178,7 +176,6 @@ def toy(tmp_path_factory):
 
 
 def test_toy_layout(toy):
-    from grout_b200.cache import KVSpec, StateSpec
     from grout_b200.config import load_config
     from grout_b200.engine.model import Model
     from grout_b200.parts import BuildContext

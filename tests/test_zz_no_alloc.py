@@ -6,7 +6,6 @@ can be used where no allocator may be called.  The check is against the
 library's ordinary entry point for the same product, on two calls in a row,
 since all calls share that scratch and the second must not see the first's
 leftovers.  The file is named to be collected last."""
-import ctypes
 from ctypes import c_int, c_void_p
 
 import pytest
