@@ -186,6 +186,11 @@ def main() -> int:
         return run_requests(args.requests, max(1, args.reps))
     W = max(args.warmup, 3)
     K = args.steps
+    most = CONTEXT - PROMPT - W - 4      # the sequences hold 2,048 prompt tokens in a context of 4,096
+    if K < 1 or K > most:
+        print(f"bench.py: --steps must be 1..{most} with --warmup {W} (prompt {PROMPT}, context "
+              f"{CONTEXT}); got {K}", file=sys.stderr)
+        return 2
     phases = set(args.phases.split(","))
     if args.no_points:
         phases.discard("points")
