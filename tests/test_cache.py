@@ -129,3 +129,51 @@ def test_slots_and_pages_are_reused_by_the_next_batch():
 
 def test_pages_for():
     assert [pages_for(n) for n in (0, 1, 64, 65, 128)] == [0, 1, 1, 2, 2]
+
+
+def test_random_batches_through_the_whole_cache():
+    """Sequences opened, grown by prompts and single tokens and closed in random order, with a
+    full store, a window store and a state store side by side: after every operation the
+    cache's own check holds, no page belongs to two sequences, and a refused request leaves
+    everything as it was."""
+    rng = random.Random(7)
+    c, _ = _cache(max_tokens=1024, max_slots=6, max_seq_len=400)
+    live = {}
+    refused = 0
+    for _ in range(3000):
+        roll = rng.random()
+        if live and roll < 0.15:
+            s = rng.choice(list(live))
+            c.close(s)
+            del live[s]
+        elif roll < 0.35:
+            try:
+                s = c.open()
+                assert s not in live
+                live[s] = 0
+            except CacheFull:
+                assert len(live) == c.max_slots
+                refused += 1
+        elif live:
+            s = rng.choice(list(live))
+            n = rng.choice([1, 1, 1, 2, 17, 64, 65, 130])
+            before = (c.tokens_held(), c.length[s])
+            try:
+                c.reserve(s, n)
+                c.advance(s, n)
+                live[s] += n
+            except CacheFull:
+                assert (c.tokens_held(), c.length[s]) == before      # nothing half done
+                refused += 1
+        c.check()
+        for store in c.stores[:2]:
+            held = [p for s in live for p in store.pages_of[s] if p is not None]
+            assert len(held) == len(set(held)) == store.pool.n_held
+        assert c.slots.n_held == len(live)
+        for s, n in live.items():
+            assert c.length[s] == n <= 400
+    assert refused > 0          # the limits were met on the way
+    for s in list(live):
+        c.close(s)
+    c.check()
+    assert c.tokens_held() == 0 and c.slots.n_held == 0 and all(st.pool.n_held == 0 for st in c.stores[:2])
