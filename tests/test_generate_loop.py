@@ -228,3 +228,54 @@ def test_looking_ahead_serves_batch_after_batch():
     outs = loop.run([Request(p, 4, stop_ids=(99,)) for p in prompts])
     assert [o.token_ids for o in outs] == [[100 + i] for i in range(5)]
     assert st.max_live <= 2 and not st.open and sorted(st.free) == [0, 1]
+
+
+def test_random_requests_in_turn_and_looking_ahead():
+    """Random prompts, budgets, stop tokens and batch limits: both ways of running a batch
+    return what the script and the rules say (a stop token ends the request and is returned
+    only on request; a budget ends it with "length"), no request runs a step beyond its
+    last token when stepping in turn, and every slot comes back."""
+    import random
+    rng = random.Random(11)
+    for trial in range(60):
+        n = rng.randint(1, 9)
+        prompts, script, reqs, want = [], [], [], []
+        for r in range(n):
+            prompt = [r + 1] * (r + 1) + [rng.randint(1, 50) for _ in range(rng.randint(0, 4))]
+            budget = rng.randint(0, 7)
+            stream = [rng.choice([99, 98] + list(range(100, 120))) for _ in range(8)]
+            stops = rng.choice([(), (99,), (99, 98)])
+            include = rng.random() < 0.3
+            prompts.append(prompt), script.append(stream)
+            reqs.append(Request(prompt, budget, stop_ids=stops, include_stop=include))
+            out, reason = [], "length"
+            for tok in stream[:budget]:
+                if tok in stops:
+                    if include:
+                        out.append(tok)
+                    reason = "stop"
+                    break
+                out.append(tok)
+            want.append((out, reason if budget else "length"))
+        max_batch = rng.randint(1, 4)
+        for make in (_loop, _ahead_loop):
+            st, loop = make(prompts, script, max_batch=max_batch, max_slots=max_batch)
+            outs = loop.run(reqs)
+            for o, (toks, reason), rq in zip(outs, want, reqs):
+                assert o.token_ids == toks, (trial, make.__name__)
+                if rq.max_new_tokens:
+                    assert o.finish_reason == reason
+                assert o.prompt_tokens == len(rq.prompt) and o.generated_tokens == len(toks)
+            assert not st.open and sorted(st.free) == list(range(max_batch))
+            assert st.max_live <= max_batch
+            if make is _loop:
+                # in turn: request r took part in one prompt step and one step per token it
+                # fed back, i.e. per generated token but the last one
+                for r, (rq, (toks, reason)) in enumerate(zip(reqs, want)):
+                    if rq.max_new_tokens == 0:
+                        assert sum(s.count(r) for s in st.steps) == 0
+                        continue
+                    fed = len(toks) - (1 if (reason == "stop" and rq.include_stop) else 0)
+                    done_by_budget = reason == "length"
+                    expect = 1 + (fed - 1 if done_by_budget else fed)
+                    assert sum(s.count(r) for s in st.steps) == max(expect, 1), (trial, r)
