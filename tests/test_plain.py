@@ -91,3 +91,31 @@ def test_plain_sampling():
     z = [math.exp(v / 0.8) for v in logits]
     for i in range(5):
         assert abs(counts[i] / 4000 - z[i] / sum(z)) < 0.03
+
+
+def test_host_sampler_follows_the_plain_sampler():
+    """The library's host-side sampler (numpy, vectorised) against the plain one, fed the
+    same logits and draws: ties, top-k, top-p, both, and a temperature at its floor."""
+    import random
+
+    import numpy as np
+
+    from grout_b200.sampling import SamplingParams
+    from grout_b200.sampling.host import choose_one
+    rng = random.Random(3)
+    g = torch.Generator().manual_seed(4)
+    for trial in range(300):
+        v = rng.choice([5, 37, 300])
+        logits = (torch.randn(v, generator=g) * rng.choice([0.5, 3.0])).float()
+        if trial % 4 == 0:                       # equal scores: index order decides
+            logits[rng.randrange(v)] = logits[rng.randrange(v)]
+            logits = (logits * 4).round() / 4
+        t = rng.choice([1e-5, 0.3, 0.8, 1.0, 2.5])
+        k = rng.choice([0, 1, 2, 7, v, v + 3])
+        p = rng.choice([1.0, 0.9, 0.5, 0.05, 0.0])
+        u = rng.random()
+        params = SamplingParams(True, t, k, p).normalised()
+        got = choose_one(np.asarray(logits), params, u)
+        want = plain_sampling.sample_next(logits.tolist(), params.temperature, params.top_k, params.top_p, u)
+        assert got == want, (trial, v, t, k, p, u)
+    assert choose_one(np.asarray([1.0, 3.0, 3.0], dtype=np.float32), SamplingParams().normalised(), 0.9) == 1
