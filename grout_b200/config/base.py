@@ -4,7 +4,11 @@ A configuration is a frozen dataclass whose field names are the keys of
 config.json.  ``ModelConfig.from_dict`` checks presence and type of every
 declared key, fills declared defaults, calls the class's ``validate`` and
 reports every problem it finds in one ``ConfigError``.  Keys that a class does
-not declare are kept in ``extra`` so that nothing of the file is lost.
+not declare are kept in ``extra`` so that nothing of the file is lost, except
+those that a class lists in ``changes_arithmetic``: a key there stands for a
+term of the model's formulas that the architecture's parts do not have, so a
+file that sets it to anything but one of its neutral values is refused instead
+of being run as if the key were absent.
 
 The reference parses the same file into ``Qwen3Config`` with serde
 (src/config.rs:6-33); it has no defaults, so a missing key is an error there.
@@ -76,6 +80,10 @@ class ModelConfig:
 
     extra: dict = field(default_factory=dict, repr=False, compare=False, kw_only=True)
 
+    #: undeclared key -> the values with which it changes nothing.  Any other
+    #: value is a problem (subclasses replace or extend the table).
+    changes_arithmetic: typing.ClassVar[dict] = {}
+
     # ---- reading -------------------------------------------------------
     @classmethod
     def from_dict(cls, raw: dict, where: str = "config.json"):
@@ -98,6 +106,13 @@ class ModelConfig:
                 values[f.name] = _coerce(v, annot)
             elif f.default is MISSING and f.default_factory is MISSING:
                 problems.append(f"required key '{f.name}' is missing")
+        for key, neutral in cls.changes_arithmetic.items():
+            if key in raw and key not in declared and \
+                    not any(raw[key] is n or (not isinstance(raw[key], bool) and n is not None
+                                              and not isinstance(n, bool) and raw[key] == n)
+                            for n in neutral):
+                problems.append(f"key '{key}'={raw[key]!r} changes the model's arithmetic and "
+                                f"this architecture has no part for it")
         if problems:
             raise ConfigError(problems, where)
         values["extra"] = {k: v for k, v in raw.items() if k not in declared}

@@ -26,7 +26,8 @@ def pytest_collection_modifyitems(config, items):
 
 
 # Tiny A and B differ in every size and option; C adds a window, a head size
-# that is no power of two and an odd number of groups.
+# that is no power of two and an odd number of groups; E is written in the other
+# form of the file.
 TINY = {
     "A": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=256,
               hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
@@ -50,8 +51,18 @@ TINY = {
               num_key_value_heads=2, head_dim=64, rope_theta=20000.0, rms_norm_eps=2e-6,
               max_position_embeddings=512, tie_word_embeddings=True, use_sliding_window=False,
               eos_token_id=199),
+    # the file as newer writers lay it out: the rotation base stands in rope_parameters
+    # only, and layer_types names each layer's kind (windowed layers that do not come
+    # last); heads of 80 in groups of one
+    "E": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=517,
+              hidden_size=112, intermediate_size=208, num_hidden_layers=3, num_attention_heads=5,
+              num_key_value_heads=5, head_dim=80, rms_norm_eps=1e-5,
+              rope_parameters={"rope_type": "default", "rope_theta": 70000.0},
+              max_position_embeddings=384, tie_word_embeddings=True, sliding_window=17,
+              layer_types=["sliding_attention", "full_attention", "sliding_attention"],
+              eos_token_id=[3, 516]),
 }
-SEEDS = {"A": 0, "B": 2, "C": 4, "D": 6}
+SEEDS = {"A": 0, "B": 2, "C": 4, "D": 6, "E": 8}
 
 
 @pytest.fixture(scope="session")

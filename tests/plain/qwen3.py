@@ -100,7 +100,7 @@ def attention_block(x, w, prefix, cfg, positions, window=None) -> torch.Tensor:
     v = (x @ w[prefix + "self_attn.v_proj.weight"].to(DT).T).reshape(T, nkv, D)
     q = rms_norm(q, w[prefix + "self_attn.q_norm.weight"], cfg["rms_norm_eps"])
     k = rms_norm(k, w[prefix + "self_attn.k_norm.weight"], cfg["rms_norm_eps"])
-    cos, sin = rope_cos_sin(positions, D, cfg["rope_theta"])
+    cos, sin = rope_cos_sin(positions, D, rope_theta(cfg))
     q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
     o = causal_attention(q, k, v, window).reshape(T, nq * D)
     return o @ w[prefix + "self_attn.o_proj.weight"].to(DT).T
@@ -114,12 +114,25 @@ def swiglu(x, w_gate, w_up, w_down) -> torch.Tensor:
     return ((g / (1.0 + torch.exp(-g))) * u) @ w_down.to(DT).T
 
 
+def rope_theta(cfg: dict) -> float:
+    """The rotation base stands in the ``rope_parameters`` object when the file
+    has one, else at the top level (src/quantized_config.rs:66-70, 79-82)."""
+    block = cfg.get("rope_parameters")
+    if isinstance(block, dict) and "rope_theta" in block:
+        return float(block["rope_theta"])
+    return float(cfg["rope_theta"])
+
+
 def layer_window(cfg: dict, layer: int):
-    """Which layers look through a window is read from config.json's
-    ``use_sliding_window``, ``sliding_window`` and ``max_window_layers``: layers
-    with index >= max_window_layers see only the last ``sliding_window`` keys.
-    The reference refuses such configs (src/model.rs:1323-1326); the rule is the
-    documented meaning of those keys."""
+    """Which layers look through a window: ``layer_types[layer]`` when the file
+    names the kind of every layer (src/quantized_config.rs:116-125 reads that
+    list), else ``use_sliding_window``, ``sliding_window`` and
+    ``max_window_layers``: layers with index >= max_window_layers see only the
+    last ``sliding_window`` keys.  The reference refuses windowed layers
+    (src/model.rs:1323-1326); the rule is the documented meaning of those keys."""
+    kinds = cfg.get("layer_types")
+    if kinds:
+        return int(cfg["sliding_window"]) if kinds[layer] == "sliding_attention" else None
     if not cfg.get("use_sliding_window", False):
         return None
     if layer < int(cfg.get("max_window_layers", cfg["num_hidden_layers"])):

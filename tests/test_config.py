@@ -21,11 +21,11 @@ def test_reads_every_key_of_config_json():
 
 
 def test_defaults_and_derived_values():
-    raw = {k: v for k, v in TINY["A"].items() if k not in ("head_dim", "rope_theta", "rms_norm_eps",
+    raw = {k: v for k, v in TINY["A"].items() if k not in ("head_dim", "rms_norm_eps",
                                                           "tie_word_embeddings", "eos_token_id")}
     cfg = Qwen3Config.from_dict(raw)
     assert cfg.head_dim == raw["hidden_size"] // raw["num_attention_heads"]
-    assert cfg.rope_theta == 1e6 and cfg.rms_norm_eps == 1e-6 and cfg.tie_word_embeddings is False
+    assert cfg.rms_norm_eps == 1e-6 and cfg.tie_word_embeddings is False
     assert cfg.eos_token_ids() == ()
     assert Qwen3Config.from_dict(TINY["B"]).eos_token_ids() == (7, 383)
     assert Qwen3Config.from_dict(dict(TINY["A"], rope_theta=10000)).rope_theta == 10000.0
@@ -49,6 +49,21 @@ def test_all_problems_are_reported_at_once():
     (dict(attention_bias=True), "attention_bias"),
     (dict(rope_scaling={"rope_type": "yarn", "factor": 4.0}), "rope_scaling"),
     (dict(use_sliding_window=True), "sliding_window"),
+    (dict(use_sliding_window=True, sliding_window=8), "max_window_layers"),
+    (dict(rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0}), "yarn"),
+    (dict(rope_parameters={"rope_theta": 5e6}), "disagrees"),
+    (dict(rope_parameters={"rope_theta": 10000.0, "partial_rotary_factor": 0.5}), "partial"),
+    (dict(rope_parameters={"full_attention": {"rope_theta": 10000.0}}), "per layer type"),
+    (dict(layer_types=["full_attention"]), "entries"),
+    (dict(layer_types=["full_attention", "linear_attention"]), "linear_attention"),
+    (dict(layer_types=["full_attention", "sliding_attention"]), "disagrees"),
+    (dict(layer_types=["full_attention", "sliding_attention"], use_sliding_window=True,
+          max_window_layers=1), "positive 'sliding_window'"),
+    (dict(partial_rotary_factor=0.25), "partial_rotary_factor"),
+    (dict(mlp_bias=True), "mlp_bias"),
+    (dict(attn_logit_softcapping=50.0), "attn_logit_softcapping"),
+    (dict(use_qk_norm=False), "use_qk_norm"),
+    (dict(num_experts=8), "num_experts"),
     (dict(num_hidden_layers=0), "positive"),
     (dict(rms_norm_eps=0.0), "rms_norm_eps"),
 ])
@@ -58,10 +73,50 @@ def test_refuses_what_the_architecture_does_not_define(change, word):
     assert word in str(e.value)
 
 
+def test_the_rotation_base_is_never_guessed():
+    raw = {k: v for k, v in TINY["A"].items() if k != "rope_theta"}
+    with pytest.raises(ConfigError) as e:           # src/config.rs:16: required
+        Qwen3Config.from_dict(raw)
+    assert "rope_theta" in str(e.value)
+    # the form that newer writers of this file use (src/quantized_config.rs:66-83)
+    cfg = Qwen3Config.from_dict(dict(raw, rope_parameters={"rope_type": "default",
+                                                           "rope_theta": 250000}))
+    assert cfg.rope_theta == 250000.0
+    both = Qwen3Config.from_dict(dict(TINY["A"], rope_parameters={"rope_theta": 10000.0}))
+    assert both.rope_theta == 10000.0
+
+
+def test_a_file_in_the_newer_form_is_read_or_refused_never_misread():
+    """rope_parameters of another type together with a windowed layer_types once
+    loaded and ran with a guessed base, no scaling and no window."""
+    raw = {k: v for k, v in TINY["A"].items() if k not in ("rope_theta", "use_sliding_window")}
+    raw.update(rope_parameters={"rope_type": "yarn", "rope_theta": 5e6, "factor": 2.0},
+               layer_types=["full_attention", "sliding_attention"])
+    with pytest.raises(ConfigError) as e:
+        Qwen3Config.from_dict(raw)
+    assert "yarn" in str(e.value) and "sliding_window" in str(e.value)
+    raw.update(rope_parameters={"rope_type": "default", "rope_theta": 5e6}, sliding_window=24)
+    cfg = Qwen3Config.from_dict(raw)
+    assert cfg.rope_theta == 5e6
+    assert [cfg.window_of_layer(i) for i in range(2)] == [None, 24]
+
+
+def test_neutral_values_of_foreign_terms_are_accepted():
+    cfg = Qwen3Config.from_dict(dict(TINY["A"], mlp_bias=False, attn_logit_softcapping=None,
+                                     partial_rotary_factor=1.0, num_experts=0, use_qk_norm=True))
+    assert cfg.extra["mlp_bias"] is False
+
+
 def test_window_per_layer():
     cfg = Qwen3Config.from_dict(TINY["C"])
     assert [cfg.window_of_layer(i) for i in range(4)] == [None, 40, 40, 40]
     assert Qwen3Config.from_dict(TINY["A"]).window_of_layer(1) is None
+    kinds = ["sliding_attention", "full_attention", "sliding_attention", "full_attention"]
+    raw = {k: v for k, v in TINY["C"].items() if k not in ("use_sliding_window", "max_window_layers")}
+    cfg = Qwen3Config.from_dict(dict(raw, layer_types=kinds))
+    assert [cfg.window_of_layer(i) for i in range(4)] == [40, None, 40, None]
+    agree = dict(TINY["C"], layer_types=["full_attention"] + ["sliding_attention"] * 3)
+    assert [Qwen3Config.from_dict(agree).window_of_layer(i) for i in range(4)] == [None, 40, 40, 40]
 
 
 def test_unknown_keys_survive_a_round_trip():

@@ -9,7 +9,8 @@ from plain import qwen3 as plain
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"A": [5, 70, 128], "B": [1, 7, 64, 150], "C": [33, 130, 300], "D": [3, 129, 400]}
+LENGTHS = {"A": [5, 70, 128], "B": [1, 7, 64, 150], "C": [33, 130, 300], "D": [3, 129, 400],
+           "E": [2, 100, 200]}
 
 
 @pytest.fixture(scope="module")
