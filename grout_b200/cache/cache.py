@@ -2,8 +2,9 @@
 layers, each sequence with its own length.
 
 ``CacheLayout`` is derived from the model's layers: every layer that owns a
-cache names what it needs (``KVSpec`` or ``StateSpec``); layers with equal
-needs share a store (and, for keys and values, one block table).  A layer that
+cache names what it needs (``KVSpec``, ``StateSpec`` or a spec of its own with a
+``make_store`` method); layers with equal needs share a store, which the spec
+makes (and, for keys and values, one block table).  A layer that
 reads another layer's cache owns nothing and is given that layer's view.
 
 ``SequenceCache.open()`` hands out a slot, ``reserve`` grows it before a step,
@@ -12,25 +13,25 @@ reads another layer's cache owns nothing and is given that layer's view.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence, Tuple, Union
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from .slots import SlotList
-from .spec import CacheFull, KVSpec, StateSpec
-from .stores import KVStore, StateStore, pages_for
+from .spec import CacheFull, StoreSizes
+from .stores import pages_for
 
 
 @dataclass
 class CacheLayout:
     """groups[g] = (spec, [owner layer indices]); where[layer] = (g, index in group)."""
-    groups: List[Tuple[Union[KVSpec, StateSpec], List[int]]]
+    groups: List[Tuple[Any, List[int]]]
     where: Dict[int, Tuple[int, int]]
 
     @staticmethod
-    def from_specs(specs: Sequence[Optional[Union[KVSpec, StateSpec]]]) -> "CacheLayout":
+    def from_specs(specs: Sequence[Optional[Any]]) -> "CacheLayout":
         """``specs[i]`` is what layer i owns (None: nothing)."""
-        groups: List[Tuple[Union[KVSpec, StateSpec], List[int]]] = []
+        groups: List[Tuple[Any, List[int]]] = []
         where: Dict[int, Tuple[int, int]] = {}
         for layer, spec in enumerate(specs):
             if spec is None:
@@ -58,16 +59,15 @@ class SequenceCache:
         self.max_slots = min(max_slots, n_pages)
         self.slots = SlotList(self.max_slots)
         self.length: Dict[int, int] = {}
-        self.stores: List[Union[KVStore, StateStore]] = []
-        per_seq = min(pages_for(max_seq_len), n_pages)
+        self.stores: List[Any] = []
+        self.sizes = StoreSizes(n_pages=n_pages, max_slots=self.max_slots,
+                                max_pages_per_seq=min(pages_for(max_seq_len), n_pages),
+                                max_seq_len=max_seq_len)
         for spec, members in layout.groups:
-            if isinstance(spec, KVSpec):
-                self.stores.append(KVStore(spec, len(members), n_pages, self.max_slots, per_seq,
-                                           dtype, device, allocate))
-            elif isinstance(spec, StateSpec):
-                self.stores.append(StateStore(spec, len(members), self.max_slots, device, allocate))
-            else:
-                raise TypeError(f"unknown cache need {spec!r}")
+            if not callable(getattr(spec, "make_store", None)):
+                raise TypeError(f"cache need {spec!r} has no make_store(n_layers, sizes, dtype, "
+                                f"device, allocate)")
+            self.stores.append(spec.make_store(len(members), self.sizes, dtype, device, allocate))
 
     # -- sequences ---------------------------------------------------------
     def open(self) -> int:

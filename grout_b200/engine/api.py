@@ -22,7 +22,7 @@ from .. import architectures  # noqa: F401  (registers the known architectures)
 from ..cache import SequenceCache
 from ..config import GenerationConfig, load_config, resolve_architecture
 from ..kernels import build as kernel_build
-from ..parts.base import BuildContext
+from ..parts.base import BuildContext, ProductChoice
 from ..weights import DictSource, FolderSource, load_params, random_tensor
 from ..sampling import DeviceSampler, HostSampler, SamplingParams
 from .batch import make_context
@@ -76,11 +76,11 @@ class Engine:
 
     # -- construction --------------------------------------------------------
     @classmethod
-    def _build(cls, arch, config, source, dtype, device, **kw) -> "Engine":
+    def _build(cls, arch, config, source, dtype, device, products=None, **kw) -> "Engine":
         dtype, device = _dtype(dtype), _device(device)
         torch.cuda.set_device(device)
         plan = arch.plan(config)
-        model = Model(plan, BuildContext(dtype, device))
+        model = Model(plan, BuildContext(dtype, device, products or ProductChoice()))
         get = load_params(model.expected(), source, dtype, device)
         with torch.cuda.device(device):
             model.load(get)
@@ -91,11 +91,13 @@ class Engine:
 
     @classmethod
     def load(cls, model_dir: str, dtype="bfloat16", device="cuda:0", *, max_tokens=None,
-             max_batch: int = 64, max_seq_len=None, use_graphs=None) -> "Engine":
+             max_batch: int = 64, max_seq_len=None, use_graphs=None,
+             products: Optional[ProductChoice] = None) -> "Engine":
         """A model folder: config.json chooses the architecture, the safetensors
-        file(s) give the weights."""
+        file(s) give the weights.  ``products`` names the kernels of the linear
+        layers (``parts.ProductChoice``; None: the defaults)."""
         arch, config = load_config(model_dir)
-        return cls._build(arch, config, FolderSource(model_dir), dtype, device,
+        return cls._build(arch, config, FolderSource(model_dir), dtype, device, products=products,
                           max_tokens=max_tokens, max_batch=max_batch, max_seq_len=max_seq_len,
                           use_graphs=use_graphs,
                           generation_config=GenerationConfig.from_model_dir(model_dir))
@@ -157,7 +159,8 @@ class Engine:
              want: Optional[Sequence[Sequence[int]]] = None) -> Optional[torch.Tensor]:
         """entries: (slot, next tokens) per sequence; want: per entry, the places
         among its tokens whose logits are returned ([n_wanted, vocab], float32, in
-        the order of the entries and of ``want``).  None when nothing is wanted."""
+        the order of the entries and of ``want``).  None when nothing is wanted.
+        The tensor returned is the caller's: later steps do not change it."""
         if not entries:
             raise ValueError("a step needs at least one sequence")
         want = [list(w) for w in want] if want is not None else [[] for _ in entries]
@@ -173,6 +176,10 @@ class Engine:
             bad = [t for t in toks if not 0 <= int(t) < self.vocab_size]
             if bad:
                 raise ValueError(f"token {bad[0]} is outside the vocabulary of {self.vocab_size}")
+        for i, ((_slot, toks), w) in enumerate(zip(entries, want)):
+            for p in w:
+                if not 0 <= int(p) < len(toks):
+                    raise ValueError(f"wanted place {p} is outside the {len(toks)} tokens of entry {i}")
         for slot, toks in entries:
             self.cache.reserve(slot, len(toks))
         self.cache.flush()
@@ -182,12 +189,12 @@ class Engine:
         started = self.profile.begin() if self.profile else None
         with torch.cuda.device(self.device):
             if graph is not None:
-                all_rows = graph.run(packed)
+                all_rows = graph.run(packed)      # the graph's own buffer: the next replay rewrites it
                 idx = [i for i, w in enumerate(want) for _p in w]
                 if not idx:
                     logits = None
-                elif idx == list(range(all_rows.shape[0])):
-                    logits = all_rows
+                elif idx == list(range(len(idx))):
+                    logits = all_rows[:len(idx)].clone()
                 else:
                     logits = all_rows[torch.tensor(idx, device=self.device)]
             else:

@@ -40,10 +40,26 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
+class ProductChoice:
+    """Which kernels a linear layer's products run on (``parts.linear.Linear``
+    explains the names).  It is an argument of every ``Linear``; parts hand on
+    the one in their ``BuildContext``."""
+    decode: str = "tc"            # "tc" | "skinny": the product for up to 64 rows
+    prefill: str = "auto"         # "auto" | "library" | "pair" | "tc": the product for more rows
+
+    def __post_init__(self):
+        if self.decode not in ("tc", "skinny"):
+            raise ValueError(f"decode product '{self.decode}': 'tc' or 'skinny'")
+        if self.prefill not in ("auto", "library", "pair", "tc"):
+            raise ValueError(f"prefill product '{self.prefill}': 'auto', 'library', 'pair' or 'tc'")
+
+
+@dataclass(frozen=True)
 class BuildContext:
-    """Where and in which precision a part computes."""
+    """Where, in which precision and on which product kernels a part computes."""
     dtype: torch.dtype            # torch.bfloat16 or torch.float32
     device: torch.device
+    products: ProductChoice = ProductChoice()
 
 
 class Part:

@@ -46,10 +46,10 @@ class SwiGLU(FeedForward):
         if self.interleave:
             k = self.interleave
             fused = torch.stack([g.view(-1, k, self.hidden), u.view(-1, k, self.hidden)], dim=1)
-            self.gate_up = Linear(fused.reshape(2 * self.intermediate, self.hidden))
+            self.gate_up = Linear(fused.reshape(2 * self.intermediate, self.hidden), self.ctx.products)
         else:
-            self.gate_up = Linear(torch.cat([g, u], dim=0))
-        self.down = Linear(params["down_proj.weight"])
+            self.gate_up = Linear(torch.cat([g, u], dim=0), self.ctx.products)
+        self.down = Linear(params["down_proj.weight"], self.ctx.products)
 
     def kernel_modules(self):
         return ("elementwise",) + self.gate_up.kernel_modules() + self.down.kernel_modules()

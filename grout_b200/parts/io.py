@@ -62,10 +62,10 @@ class LinearHead(Head):
 
     def load(self, params):
         if not self.tied:
-            self.proj = Linear(params["weight"])
+            self.proj = Linear(params["weight"], self.ctx.products)
 
     def tie(self, table: torch.Tensor) -> None:
-        self.proj = Linear(table)   # shares the allocation (src/model.rs:1375-1377)
+        self.proj = Linear(table, self.ctx.products)   # shares the allocation (src/model.rs:1375-1377)
 
     def kernel_modules(self):
         return self.proj.kernel_modules() if self.proj else ()

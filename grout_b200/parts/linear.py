@@ -7,9 +7,9 @@ It picks the product by the weight's precision and by the number of rows:
   checkpoint stores in 32-bit is used in 32-bit.
 * bf16 weight, up to 64 rows (every decode step): the TMA-fed tcgen05 product
   with the weight rows on the 128-row side of the MMA (``gemm_tc_bf16`` with
-  ``swap``), or, for ``decode_kernel = "skinny"``, the mma.sync weight-streaming
+  ``swap``), or, for ``products.decode = "skinny"``, the mma.sync weight-streaming
   kernel (``gemm_skinny_bf16``).
-* bf16 weight, more rows (a prompt): ``prefill_kernel = "auto"`` takes the product
+* bf16 weight, more rows (a prompt): ``products.prefill = "auto"`` takes the product
   on pairs of SMs (``gemm_tc2_bf16``, tcgen05.mma.cta_group::2) where it is at
   least as fast as the library's product, which is when its 256 x 256 tiles fill
   at least two rounds on the GPU's pairs of SMs (the qkv product and the fused
@@ -28,13 +28,15 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
+from .base import ProductChoice
 
 
 class Linear:
-    decode_kernel = "tc"          # "tc" | "skinny": the product for up to 64 rows
-    prefill_kernel = "auto"       # "auto" | "library" | "pair" | "tc": the product for more rows
-
-    def __init__(self, weight: torch.Tensor):
+    def __init__(self, weight: torch.Tensor, products: Optional[ProductChoice] = None):
+        """``products``: which kernels take the products (a part passes
+        ``ctx.products``); None means the defaults."""
+        products = products or ProductChoice()
+        self.decode_kernel, self.prefill_kernel = products.decode, products.prefill
         if weight.dim() != 2:
             raise ValueError(f"a linear weight is [out, in], got {tuple(weight.shape)}")
         if weight.dtype not in (torch.float32, torch.bfloat16):

@@ -92,8 +92,8 @@ class GQAAttention(Mixer):
             ws += [params["k_proj.weight"], params["v_proj.weight"]]
         if len({w.dtype for w in ws}) != 1:
             raise ValueError("q, k and v projections must be stored in one dtype to be fused")
-        self.qkv = Linear(torch.cat(ws, dim=0) if len(ws) > 1 else ws[0])
-        self.o = Linear(params["o_proj.weight"])
+        self.qkv = Linear(torch.cat(ws, dim=0) if len(ws) > 1 else ws[0], self.ctx.products)
+        self.o = Linear(params["o_proj.weight"], self.ctx.products)
         if self.qk_norm_eps is not None:
             self.q_norm_w = params["q_norm.weight"].contiguous()
             if not self.shares_kv:

@@ -7,7 +7,10 @@
 * ``apply_qk(q, k, token_pos) -> (q, k)``: any other encoding of queries and
   keys ([T, heads, D]); attention calls it between its projection and the
   cache write when ``rotary()`` is None.
-* ``apply_embeddings(x, token_pos) -> x``: encodings added to the embeddings.
+
+An encoding that is added to the embeddings is not of this family: it is an
+``embedding`` part, whose ``forward(tokens, step)`` has every row's position in
+``step.token_pos``.
 """
 from __future__ import annotations
 
@@ -34,9 +37,6 @@ class PositionEncoding(Part):
 
     def apply_qk(self, q, k, token_pos):
         return q, k
-
-    def apply_embeddings(self, x, token_pos):
-        return x
 
 
 @register_part("position", "none")

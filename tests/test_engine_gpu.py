@@ -124,15 +124,16 @@ def test_padding_changes_nothing(engines):
     assert torch.equal(outs[0], outs[1])
 
 
-def test_prompt_products_on_pairs_of_sms_inside_the_engine(model_dirs, oracle, monkeypatch):
+def test_prompt_products_on_pairs_of_sms_inside_the_engine(model_dirs, oracle):
     """With every prompt product on the 2-SM tcgen05 kernel (which the default only
     takes at sizes a tiny model never reaches): whole prompts, the tail decoded, and a
     batch, against the plain implementation."""
     from grout_b200.engine import Engine
     from grout_b200.kernels import ops
-    from grout_b200.parts import Linear
-    monkeypatch.setattr(Linear, "prefill_kernel", "pair")
-    eng = Engine.load(model_dirs["D"], dtype="bfloat16", max_tokens=4096, max_batch=8, max_seq_len=512)
+    from grout_b200.parts import ProductChoice
+    eng = Engine.load(model_dirs["D"], dtype="bfloat16", max_tokens=4096, max_batch=8, max_seq_len=512,
+                      products=ProductChoice(prefill="pair"))
+    assert eng.model.blocks[0].mixer.qkv.prefill_kernel == "pair"
     reqs = [random_tokens(n, TINY["D"]["vocab_size"], 880 + n) for n in (400, 129, 70)]
     for r in reqs[:2]:
         assert_close(run_whole(eng, r), oracle("D", r), "bfloat16", "pair products, whole")

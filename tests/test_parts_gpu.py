@@ -86,12 +86,12 @@ def test_swiglu_part(dtype):
 def test_swiglu_part_with_every_prompt_product(kernel):
     """The feed-forward of a prompt through each of the products a Linear can be told
     to use; "pair" fuses SiLU into the gate|up product on pairs of SMs."""
-    from grout_b200.parts import Linear, PartSpec, build_part
-    ff = build_part("feedforward", PartSpec("swiglu", dict(hidden=96, intermediate=208)), _ctx("bfloat16"))
+    from grout_b200.parts import BuildContext, PartSpec, ProductChoice, build_part
+    ctx = BuildContext(torch.bfloat16, DEV, ProductChoice(prefill=kernel))
+    ff = build_part("feedforward", PartSpec("swiglu", dict(hidden=96, intermediate=208)), ctx)
     p = _params(ff, 12, "bfloat16")
     _load(ff, p, "bfloat16")
-    ff.gate_up.prefill_kernel = ff.down.prefill_kernel = kernel
-    assert Linear.prefill_kernel == "auto"
+    assert ff.gate_up.prefill_kernel == ff.down.prefill_kernel == kernel
     for rows in (65, 300):
         x = _rand((rows, 96), 13 + rows).to(torch.bfloat16)
         got = ff.forward(x.to(DEV), None)
