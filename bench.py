@@ -263,7 +263,7 @@ def main() -> int:
         torch.cuda.synchronize()
         ms = a.elapsed_time(b)
         launches = ops.launch_count() - before
-        graph = eng.graphs.get(batch)
+        graph = eng.graphs.decode(batch, PROMPT + warm + steps + 1)
         if graph is not None and graph.graph is not None:
             launches += steps * graph.kernels_per_replay
         ctx_mid = PROMPT + warm + steps / 2.0
@@ -292,7 +292,7 @@ def main() -> int:
         eng.generate(prompts, 4, ignore_eos=True)              # warm-up
         outs = eng.generate(prompts, n_new, ignore_eos=True)
         e2e_tps = sum(o.generated_tokens - 1 for o in outs) / outs[0].decode_elapsed
-        graph = eng.graphs.get(args.batch)
+        graph = eng.graphs.decode(args.batch, PROMPT + n_new)
         h2d = int(graph.dev.numel() * 4) if graph is not None else 0
         e2e = {"value": round(e2e_tps, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": 4 * args.batch}

@@ -8,9 +8,13 @@
 // The reference's rms_norm_f16 (src/kernels.rs:304-343) and add_rms_norm_f16
 // (src/kernels.rs:3013-3074) keep the sum in f32 only inside the kernel and
 // store a 16-bit residual; here the residual stream itself stays 32-bit.
-// The reduction tree depends on N only, so a row's result does not depend on
-// the batch it is in.
+// In 32-bit the kernel, and with it the reduction tree, is chosen by N only, so
+// a row's result does not depend on the batch it is in; in bfloat16 few rows of a
+// wide model take a cluster of blocks per row (another order of sums, which
+// bfloat16's rounding of y hides).
 #include <cooperative_groups.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -254,7 +258,13 @@ static int launch(const float* res_in, const void* delta, const float* parts, in
   const bool aligned = ((((uintptr_t)res_in) | ((uintptr_t)delta) | ((uintptr_t)w) |
                          ((uintptr_t)res_out) | ((uintptr_t)y) | ((uintptr_t)parts) |
                          ((uintptr_t)(part_stride * 4))) & 15) == 0;
-  if (aligned && n_rows <= 64 && N >= 1024 && N % (4 * NC_CLUSTER) == 0 && N / NC_CLUSTER <= 4096) {
+  // The cluster kernel is chosen by the number of rows and sums in another order
+  // than the kernels below.  The 32-bit path never takes it: there the order of
+  // a row's sums may depend on the width alone, so that a token's result is the
+  // same in a step of one row and in a step of thousands.
+  constexpr bool by_rows_too = !std::is_same<T, float>::value;
+  if (by_rows_too && aligned && n_rows <= 64 && N >= 1024 && N % (4 * NC_CLUSTER) == 0 &&
+      N / NC_CLUSTER <= 4096) {
     int threads = ((N / NC_CLUSTER / 4 + 31) / 32) * 32;
     return gb_launch_cluster(add_rmsnorm_cluster_kernel<T, WT>, dim3(n_rows * NC_CLUSTER),
                              dim3(threads), 0, stream, NC_CLUSTER, res_in, (const T*)delta, parts,

@@ -27,7 +27,7 @@ from ..weights import DictSource, FolderSource, load_params, random_tensor
 from ..sampling import DeviceSampler, HostSampler, SamplingParams
 from .batch import make_context
 from .generate import GenerationLoop, GenerationOutput, Request
-from .graphs import DecodeGraphs
+from .graphs import StepGraphs
 from .model import Model
 from .profile import StepProfile
 
@@ -68,7 +68,7 @@ class Engine:
                                    max_slots=max_batch, max_seq_len=self.max_seq_len,
                                    dtype=dtype, device=device)
         self.use_graphs = (dtype == torch.bfloat16) if use_graphs is None else bool(use_graphs)
-        self.graphs = DecodeGraphs(model, self.cache, device)
+        self.graphs = StepGraphs(model, self.cache, device)
         self.vocab_size = plan.vocab_size
         self.max_batch = self.cache.max_slots
         self.profile: Optional[StepProfile] = None
@@ -185,10 +185,15 @@ class Engine:
         self.cache.flush()
         packed = [(slot, self.cache.length[slot], list(toks)) for slot, toks in entries]
         decode = all(len(t) == 1 for _s, t in entries)
-        graph = self.graphs.get(len(entries)) if (decode and self.use_graphs) else None
+        graph = None
+        if self.use_graphs and decode:
+            graph = self.graphs.decode(len(entries), max(s + 1 for _slot, s, _t in packed))
+        elif self.use_graphs:
+            graph = self.graphs.prompt(sum(len(t) for _s, t in entries), len(entries),
+                                       sum(len(w) for w in want))
         started = self.profile.begin() if self.profile else None
         with torch.cuda.device(self.device):
-            if graph is not None:
+            if graph is not None and decode:
                 all_rows = graph.run(packed)      # the graph's own buffer: the next replay rewrites it
                 idx = [i for i, w in enumerate(want) for _p in w]
                 if not idx:
@@ -197,6 +202,9 @@ class Engine:
                     logits = all_rows[:len(idx)].clone()
                 else:
                     logits = all_rows[torch.tensor(idx, device=self.device)]
+            elif graph is not None:
+                logits = graph.run(packed, want)
+                logits = logits.clone() if logits is not None else None
             else:
                 ctx = make_context(packed, want, self.device)
                 logits = self.model.forward(ctx, self.cache)
@@ -238,7 +246,7 @@ class Engine:
     def can_step_ahead(self, n: int) -> bool:
         """Whether decode steps of up to ``n`` sequences can take their tokens on
         the device (they run as captured graphs)."""
-        return bool(self.use_graphs) and self.graphs.get(n) is not None
+        return bool(self.use_graphs) and 0 < n <= self.graphs.largest
 
     def step_ahead(self, entries: Sequence[Tuple[int, int]], chosen: torch.Tensor) -> torch.Tensor:
         """One decode step whose input tokens are still on the device: entry
@@ -251,12 +259,12 @@ class Engine:
         slots = [s for s, _r in entries]
         if len(set(slots)) != len(slots):
             raise ValueError("a slot appears twice in one step")
-        graph = self.graphs.get(len(entries))
-        if graph is None or not self.use_graphs:
+        if not self.can_step_ahead(len(entries)):
             raise ValueError("this many sequences cannot step ahead: ask can_step_ahead first")
         for slot in slots:
             self.cache.reserve(slot, 1)
         self.cache.flush()
+        graph = self.graphs.decode(len(entries), max(self.cache.length[s] for s in slots) + 1)
         packed = [(slot, self.cache.length[slot], [0]) for slot in slots]
         with torch.cuda.device(self.device):
             logits = graph.run(packed, tokens_from=(getattr(chosen, "dev", chosen),

@@ -36,10 +36,21 @@ class StepContext:
     decode: bool                  # every sequence brings exactly one token
     max_q_len: int
     max_kv_len: int               # upper bound of kv_len (host knowledge)
-    # host copies, valid for eager steps only
+    # host copies, valid for eager steps only (empty in a captured step)
     q_lens: Tuple[int, ...] = ()
     starts: Tuple[int, ...] = ()
     slot_list: Tuple[int, ...] = ()
+
+    def q_blocks(self, rows: int) -> int:
+        """How many blocks of ``rows`` query rows the step's sequences make, each
+        sequence starting a block of its own: the exact count when the host knows
+        the lengths, else (a captured step, whose lengths change from replay to
+        replay) the most that ``n_tokens`` rows in ``n_seqs`` sequences can make.
+        A kernel sizes its grid with it and finds each block's sequence from
+        ``cu_q`` on the device; blocks beyond the real count find none."""
+        if self.q_lens:
+            return sum((n + rows - 1) // rows for n in self.q_lens)
+        return self.n_tokens // rows + self.n_seqs
 
 
 def layout_sizes(n_tokens: int, n_seqs: int, n_want: int):
@@ -96,6 +107,39 @@ def pack_step(entries: Sequence[Tuple[int, int, Sequence[int]]],
                 max_q_len=max(q_lens) if q_lens else 0,
                 max_kv_len=max((s + q for s, q in zip(starts, q_lens)), default=0))
     return buf, meta
+
+
+def pack_step_padded(entries: Sequence[Tuple[int, int, Sequence[int]]],
+                     want: Optional[Sequence[Sequence[int]]], n_tokens: int, n_seqs: int,
+                     n_want: int):
+    """The same layout filled up to fixed sizes, for a step that replays a captured
+    graph: after the real sequences comes, if rows are left, one padding sequence
+    (slot -1, positions from 0) that takes all of them, then sequences without
+    rows; the list of wanted rows is filled up with row 0.  Raises ValueError when
+    the entries do not fit."""
+    real_tokens = sum(len(e[2]) for e in entries)
+    filler = n_tokens - real_tokens
+    want = [list(w) for w in want] if want is not None else [[] for _ in entries]
+    real_want = sum(len(w) for w in want)
+    if filler < 0 or len(entries) + (1 if filler else 0) > n_seqs or real_want > n_want:
+        raise ValueError(f"{len(entries)} sequences with {real_tokens} tokens and {real_want} "
+                         f"wanted rows do not fit a step of {n_seqs} / {n_tokens} / {n_want}")
+    padded = list(entries) + ([(-1, 0, [0] * filler)] if filler else [])
+    empty = n_seqs - len(padded)
+    buf, meta = pack_step(padded, want + [[] for _ in range(len(padded) - len(entries))])
+    off, total = layout_sizes(n_tokens, n_seqs, n_want)
+    out = np.zeros(total, dtype=np.int32)
+    for name, (o, cnt) in meta["off"].items():
+        out[off[name][0]: off[name][0] + cnt] = buf[o:o + cnt]
+    n_in = len(padded)
+    o = off["cu_q"][0]
+    out[o + n_in + 1: o + n_seqs + 1] = n_tokens           # sequences without rows
+    o = off["slots"][0]
+    out[o + n_in: o + n_seqs] = -1
+    meta = dict(meta, off=off, n_seqs=n_seqs, n_want=n_want, n_real_want=real_want,
+                q_lens=meta["q_lens"] + (0,) * empty, starts=meta["starts"] + (0,) * empty,
+                slot_list=meta["slot_list"] + (-1,) * empty)
+    return out, meta
 
 
 def context_from(dev_buf: torch.Tensor, meta: dict) -> StepContext:

@@ -79,6 +79,12 @@ class Model:
                 mods.extend(p.kernel_modules())
         return tuple(dict.fromkeys(mods))
 
+    def captures_prompts(self) -> bool:
+        """Whether every part allows prompt steps to be captured (``Part.captures_prompts``)."""
+        return all(p.captures_prompts()
+                   for top in [self.embedding, *self.blocks, self.final_norm, self.head]
+                   for p in _walk(top))
+
     # -- forward -----------------------------------------------------------
     def forward(self, step: StepContext, cache: SequenceCache) -> Optional[torch.Tensor]:
         """Runs the step's tokens through every scheduled layer; returns 32-bit

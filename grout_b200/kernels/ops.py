@@ -587,11 +587,26 @@ def fast_attention_takes(D: int, nq: int, nkv: int, page: int) -> bool:
     return D % 16 == 0 and 16 <= D <= 128 and page == 64 and nq % nkv == 0 and nq // nkv <= 16
 
 
-def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens, page: int,
-                      scale: float, window: Optional[int] = None) -> torch.Tensor:
+def _q_blocks(q_lens, n_qblocks, rows: int, T: int, n_seqs: int) -> int:
+    """Blocks of ``rows`` query rows: counted from the host's copy of the
+    sequences' row counts, or taken as given (an upper bound; the kernels find each
+    block's sequence on the device and blocks beyond the real count do nothing)."""
+    if q_lens:
+        if sum(q_lens) != T or len(q_lens) != n_seqs:
+            raise KernelError("q_lens do not describe the step's rows")
+        return sum((n + rows - 1) // rows for n in q_lens)
+    if n_qblocks is None:
+        return T // rows + n_seqs
+    return int(n_qblocks)
+
+
+def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens=(),
+                      page: int, scale: float, window: Optional[int] = None,
+                      n_qblocks: Optional[int] = None) -> torch.Tensor:
     """Causal attention of whole prompts (or their continuation) on the tensor
-    cores.  ``q_lens`` are the host's copy of the sequences' row counts; they size
-    the grid."""
+    cores.  The grid is sized from ``q_lens``, the host's copy of the sequences'
+    row counts, or, without them, from ``n_qblocks`` (an upper bound of the
+    64-row blocks; by default the most the rows and sequences can make)."""
     T, nq, D = q.shape
     _need(q, "q", torch.bfloat16, 3)
     _need(k_pages, "k pages", torch.bfloat16, 4)
@@ -601,15 +616,16 @@ def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, 
         raise KernelError(f"pages are {tuple(k_pages.shape)}, expected [*, nkv, {page}, {D}]")
     for t, nm in ((block_table, "block table"), (cu_q, "cu_q"), (slots, "slots"), (kv_len, "kv_len")):
         _need(t, nm, torch.int32)
-    if sum(q_lens) != T or len(q_lens) != slots.shape[0]:
-        raise KernelError("q_lens do not describe the step's rows")
+    n_seqs = slots.shape[0]
+    if cu_q.shape[0] != n_seqs + 1 or kv_len.shape[0] != n_seqs:
+        raise KernelError("cu_q, slots and kv_len do not describe one list of sequences")
     out = torch.empty_like(q)
     a = _PrefillArgs()
     a.q, a.k_pages, a.v_pages, a.block_table = q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr()
     a.cu_q, a.slots, a.kv_len, a.out = cu_q.data_ptr(), slots.data_ptr(), kv_len.data_ptr(), out.data_ptr()
-    a.n_seqs, a.nq, a.nkv, a.max_pages = len(q_lens), nq, nkv, block_table.shape[1]
+    a.n_seqs, a.nq, a.nkv, a.max_pages = n_seqs, nq, nkv, block_table.shape[1]
     a.window = int(window or 0)
-    a.n_qblocks = sum((n + PREFILL_ROWS - 1) // PREFILL_ROWS for n in q_lens)
+    a.n_qblocks = _q_blocks(q_lens, n_qblocks, PREFILL_ROWS, T, n_seqs)
     a.scale_log2 = float(scale) * _LOG2E
     _check(_fn("attn_prefill_bf16", "gb_attn_prefill_bf16", "piip")(
         ctypes.addressof(a), D, page, _stream()), "attn_prefill_bf16")
@@ -625,27 +641,28 @@ class _AttnTcArgs(ctypes.Structure):
 PREFILL_TC_ROWS = 0        # query rows per block of the tcgen05 prefill kernel: 128, 256 or 0 = by size
 
 
-def prefill_tc_rows(q_lens, nq: int, device) -> int:
+def prefill_tc_rows(blocks_of_256: int, nq: int, device) -> int:
     """256 rows a block (two query blocks that share their key tiles, one block
     an SM) unless that leaves most SMs without a block; then 128 (half-size
     blocks, two an SM).  Measured on 32 heads of 128: 512 tokens 21.8 us with 128
     rows against 25.7 us with 256; from 1,024 tokens on 256 rows are faster."""
     if PREFILL_TC_ROWS:
         return PREFILL_TC_ROWS
-    blocks = sum((n + 255) // 256 for n in q_lens) * nq
-    return 256 if 5 * blocks >= 3 * _sm_count(device) else 128
+    return 256 if 5 * blocks_of_256 * nq >= 3 * _sm_count(device) else 128
 
 
 def attn_prefill_tc_takes(D: int, nq: int, nkv: int, page: int) -> bool:
     return D in (64, 128) and page == 64 and nq % nkv == 0
 
 
-def attn_prefill_tc(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens, page: int,
-                    scale: float, window: Optional[int] = None,
-                    rows_per_block: int = 0) -> torch.Tensor:
+def attn_prefill_tc(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens=(),
+                    page: int, scale: float, window: Optional[int] = None,
+                    rows_per_block: int = 0, n_qblocks: Optional[int] = None) -> torch.Tensor:
     """Causal attention of whole prompts (or their continuation) with both
     products on the tcgen05 tensor cores.  Pages must hold finite values in the
-    rows beyond a sequence's length (the cache zero-fills its pages)."""
+    rows beyond a sequence's length (the cache zero-fills its pages).  The grid is
+    sized from ``q_lens`` (the host's copy of the row counts) or, without them,
+    from ``n_qblocks``, an upper bound of the blocks of ``rows_per_block`` rows."""
     _need(q, "q", torch.bfloat16, 3)
     T, nq, D = q.shape
     _need(k_pages, "k pages", torch.bfloat16, 4)
@@ -655,17 +672,19 @@ def attn_prefill_tc(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_
         raise KernelError(f"pages are {tuple(k_pages.shape)}, expected [*, nkv, {page}, {D}]")
     for t, nm in ((block_table, "block table"), (cu_q, "cu_q"), (slots, "slots"), (kv_len, "kv_len")):
         _need(t, nm, torch.int32)
-    if sum(q_lens) != T or len(q_lens) != slots.shape[0]:
-        raise KernelError("q_lens do not describe the step's rows")
+    n_seqs = slots.shape[0]
+    if cu_q.shape[0] != n_seqs + 1 or kv_len.shape[0] != n_seqs:
+        raise KernelError("cu_q, slots and kv_len do not describe one list of sequences")
     out = torch.empty_like(q)
     a = _AttnTcArgs()
     a.block_table, a.cu_q, a.slots, a.kv_len = (block_table.data_ptr(), cu_q.data_ptr(),
                                                 slots.data_ptr(), kv_len.data_ptr())
     a.out, a.error = out.data_ptr(), _tc_error_flag(q.device).data_ptr()
-    a.n_seqs, a.nq, a.nkv, a.max_pages = len(q_lens), nq, nkv, block_table.shape[1]
+    a.n_seqs, a.nq, a.nkv, a.max_pages = n_seqs, nq, nkv, block_table.shape[1]
     a.window = int(window or 0)
-    rows = int(rows_per_block) if rows_per_block else prefill_tc_rows(q_lens, nq, q.device)
-    a.n_qblocks = sum((n + rows - 1) // rows for n in q_lens)
+    rows = int(rows_per_block) if rows_per_block else \
+        prefill_tc_rows(_q_blocks(q_lens, None, 256, T, n_seqs), nq, q.device)
+    a.n_qblocks = _q_blocks(q_lens, n_qblocks, rows, T, n_seqs)
     a.scale_log2 = float(scale) * _LOG2E
     _check(_fn("attn_prefill_tc", "gb_attn_prefill_tc", "ppppiliiip")(
         q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), ctypes.addressof(a), T,
@@ -740,15 +759,15 @@ def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float
             return attn_decode_bf16(q, k_pages, v_pages, block_table, slots=step.slots,
                                     kv_len=step.kv_len, page=page, scale=scale,
                                     max_kv_len=step.max_kv_len, window=window)
-        if step.q_lens and PREFILL_ATTENTION == "tc" and \
-                attn_prefill_tc_takes(D, nq, k_pages.shape[1], page):
+        # the grid comes from the host's copy of the lengths; a captured step has
+        # none, and the kernels then take the most blocks its rows can make
+        if PREFILL_ATTENTION == "tc" and attn_prefill_tc_takes(D, nq, k_pages.shape[1], page):
             return attn_prefill_tc(q, k_pages, v_pages, block_table, cu_q=step.cu_q,
                                    slots=step.slots, kv_len=step.kv_len, q_lens=step.q_lens,
                                    page=page, scale=scale, window=window)
-        if step.q_lens:
-            return attn_prefill_bf16(q, k_pages, v_pages, block_table, cu_q=step.cu_q,
-                                     slots=step.slots, kv_len=step.kv_len, q_lens=step.q_lens,
-                                     page=page, scale=scale, window=window)
+        return attn_prefill_bf16(q, k_pages, v_pages, block_table, cu_q=step.cu_q,
+                                 slots=step.slots, kv_len=step.kv_len, q_lens=step.q_lens,
+                                 page=page, scale=scale, window=window)
     return attn_generic(q, k_pages, v_pages, block_table, token_seq=step.token_seq,
                         token_pos=step.token_pos, slots=step.slots, page=page, scale=scale,
                         window=window)

@@ -89,6 +89,19 @@ class Part:
     def children(self) -> Tuple["Part", ...]:
         return ()
 
+    # -- captured steps -----------------------------------------------------
+    def captures_prompts(self) -> bool:
+        """Whether a prompt step through this part may be captured as a CUDA graph
+        and replayed for other prompts of the same bucket of sizes.  That holds
+        when ``forward`` queues device work only and takes everything that
+        differs between such prompts (how the rows divide into sequences, their
+        positions, lengths and slots) from the step's device arrays, never from
+        the host copies ``q_lens``, ``starts`` and ``slot_list``, which a captured
+        step leaves empty.  Rows of slot -1 and sequences without rows are
+        padding.  The default is False: the step then runs launch by launch.
+        (Decode steps are always captured; their contract is the mixer's.)"""
+        return False
+
 
 _REGISTRY: Dict[Tuple[str, str], type] = {}
 

@@ -48,6 +48,9 @@ class PreNormBlock(Block):
     def cache_spec(self):
         return self.mixer.cache_spec()
 
+    def captures_prompts(self):
+        return True
+
     def forward(self, res, pending, step, cache):
         res, n = self.norm1.add_norm(res, pending)
         a = self.mixer.forward(n, step, cache)

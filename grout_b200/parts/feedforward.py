@@ -54,5 +54,8 @@ class SwiGLU(FeedForward):
     def kernel_modules(self):
         return ("elementwise",) + self.gate_up.kernel_modules() + self.down.kernel_modules()
 
+    def captures_prompts(self):
+        return True
+
     def forward(self, x, step):
         return self.down(self.gate_up.silu_mul(x, self.interleave), partial_ok=True)

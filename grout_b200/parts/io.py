@@ -35,6 +35,9 @@ class TokenEmbedding(Embedding):
     def kernel_modules(self):
         return ("embed", "elementwise")
 
+    def captures_prompts(self):
+        return True
+
     def forward(self, tokens, step):
         x = ops.embed(self.weight, tokens)
         return ops.cast(x, self.ctx.dtype) if x.dtype != self.ctx.dtype else x
@@ -69,6 +72,9 @@ class LinearHead(Head):
 
     def kernel_modules(self):
         return self.proj.kernel_modules() if self.proj else ()
+
+    def captures_prompts(self):
+        return True
 
     def forward(self, h):
         return self.proj(h, out_dtype=torch.float32)

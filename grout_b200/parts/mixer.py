@@ -108,6 +108,11 @@ class GQAAttention(Mixer):
     def cache_spec(self):
         return None if self.shares_kv else KVSpec(self.nkv, self.D, self.window)
 
+    def captures_prompts(self):
+        # an encoding with arithmetic of its own runs between two kernels here and
+        # answers for itself
+        return True
+
     def forward(self, x, step, cache):
         T = x.shape[0]
         rot = self.position.rotary()

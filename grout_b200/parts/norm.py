@@ -64,6 +64,9 @@ class RMSNorm(Norm):
     def kernel_modules(self):
         return ("norm",)
 
+    def captures_prompts(self):
+        return True
+
     def forward(self, x):
         _res, y = ops.add_rmsnorm(None, x, self.weight, self.eps, dtype=self.ctx.dtype,
                                   write_res=False)

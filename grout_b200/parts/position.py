@@ -44,6 +44,9 @@ class NoPosition(PositionEncoding):
     def __init__(self, ctx: BuildContext):
         super().__init__(ctx)
 
+    def captures_prompts(self):
+        return True
+
 
 @register_part("position", "rotary_half_split")
 class RotaryHalfSplit(PositionEncoding):
@@ -68,3 +71,6 @@ class RotaryHalfSplit(PositionEncoding):
 
     def rotary(self):
         return self._table
+
+    def captures_prompts(self):
+        return True

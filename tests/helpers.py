@@ -80,3 +80,51 @@ def run_batch(engine, requests, prompt_lens):
         for s in slots:
             if s is not None:
                 engine.close_sequence(s)
+
+
+def run_chunks(engine, tokens, chunks):
+    """One request alone, its tokens fed in steps of the given sizes (which must
+    add up to its length), logits everywhere."""
+    assert sum(chunks) == len(tokens)
+    s = engine.open_sequence()
+    try:
+        rows, o = [], 0
+        for n in chunks:
+            rows.append(engine.step([(s, tokens[o:o + n])], [list(range(n))]).float().cpu())
+            o += n
+        return torch.cat(rows, 0)
+    finally:
+        engine.close_sequence(s)
+
+
+def run_schedule(engine, requests, schedule):
+    """``schedule``: a list of steps, each a dict request index -> number of tokens
+    that request brings in that step (a request may be absent from a step, start in
+    a later one, bring one token while another brings many).  Every request's
+    tokens must be used up by the end.  Returns logits of every position of every
+    request; a request's slot is given back after its last token."""
+    slots, cursor = {}, [0] * len(requests)
+    out = [[] for _ in requests]
+    try:
+        for stepno, bring in enumerate(schedule):
+            entries, want, order = [], [], []
+            for i, n in bring.items():
+                if i not in slots:
+                    assert cursor[i] == 0
+                    slots[i] = engine.open_sequence()
+                entries.append((slots[i], requests[i][cursor[i]:cursor[i] + n]))
+                want.append(list(range(n)))
+                order.append((i, n))
+            logits = engine.step(entries, want).float().cpu()
+            o = 0
+            for i, n in order:
+                out[i].append(logits[o:o + n])
+                o += n
+                cursor[i] += n
+                if cursor[i] == len(requests[i]):
+                    engine.close_sequence(slots.pop(i))
+        assert cursor == [len(r) for r in requests], "the schedule does not use every token"
+        return [torch.cat(o, 0) for o in out]
+    finally:
+        for s in slots.values():
+            engine.close_sequence(s)

@@ -3,7 +3,8 @@ import pytest
 import torch
 
 from conftest import TINY, random_tokens
-from helpers import assert_close, run_batch, run_tail_decoded, run_whole
+from helpers import (assert_close, run_batch, run_chunks, run_schedule, run_tail_decoded,
+                     run_whole)
 from plain import qwen3 as plain
 
 pytestmark = pytest.mark.gpu
@@ -90,6 +91,132 @@ def test_first_tokens_and_long_decoding(engines, oracle, dtype):
     eng = engines("B", dtype)
     toks = random_tokens(141, TINY["B"]["vocab_size"], 400)
     assert_close(run_tail_decoded(eng, toks, tail=140), oracle("B", toks), dtype, "long decoding")
+
+
+def _chunkings(name):
+    """Ways of cutting a prompt: tiny pieces; pieces that end one short of a page,
+    on it and beyond it; pieces that cross the 64-token page twice."""
+    if TINY[name]["max_position_embeddings"] < 140:
+        return [[2, 1, 4], [63, 1, 62, 2], [60, 10, 58]]
+    return [[2, 1, 4], [63, 1, 64, 2], [60, 10, 70]]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_a_prompt_fed_in_chunks(engines, oracle, name, dtype):
+    """A sequence continued with more than one token: the step packs rows whose
+    positions start beyond zero, attention reads keys of earlier steps and of this
+    one, and a slot may grow by several pages in one step.  (The reference holds its
+    engine to chunked == whole: src/bin/grout_quant_probe.rs:7-60.)"""
+    eng = engines(name, dtype)
+    for i, chunks in enumerate(_chunkings(name)):
+        toks = random_tokens(sum(chunks), TINY[name]["vocab_size"], 700 + i)
+        got = run_chunks(eng, toks, chunks)
+        assert_close(got, oracle(name, toks), dtype, f"{name} chunks {chunks}")
+        if dtype == "float32":
+            assert (got - run_whole(eng, toks)).abs().max().item() < 2e-6, chunks
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
+def _mixed_schedule():
+    """Request 0 starts with 20 tokens and goes on with 5 at once; request 1 starts
+    with 9 and brings one token at a time; request 2 joins in the third step with 70
+    tokens while the others continue; later steps mix one and several tokens, and the
+    requests end at different steps."""
+    lengths = [20 + 5 + 1 + 3 + 1, 9 + 1 + 1 + 1 + 1 + 1, 70 + 1 + 2]
+    schedule = [{0: 20, 1: 9}, {0: 5, 1: 1}, {0: 1, 1: 1, 2: 70}, {0: 3, 1: 1, 2: 1},
+                {0: 1, 1: 1, 2: 2}, {1: 1}]
+    return lengths, schedule
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_steps_that_mix_one_and_many_tokens(engines, oracle, name, dtype):
+    eng = engines(name, dtype)
+    lengths, schedule = _mixed_schedule()
+    reqs = [random_tokens(n, TINY[name]["vocab_size"], 720 + i) for i, n in enumerate(lengths)]
+    got = run_schedule(eng, reqs, schedule)
+    for i, r in enumerate(reqs):
+        assert_close(got[i], oracle(name, r), dtype, f"{name} mixed steps, request {i}")
+        if dtype == "float32":
+            assert (got[i] - run_whole(eng, r)).abs().max().item() < 2e-6, i
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
+@pytest.fixture(scope="module")
+def wide_engines(model_dirs):
+    """Engines with room for 64 sequences at once (graph buckets 32 and 64)."""
+    from grout_b200.engine import Engine
+    made = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in made:
+            made[(name, dtype)] = Engine.load(model_dirs[name], dtype=dtype, max_tokens=64 * 128,
+                                              max_batch=64, max_seq_len=128)
+        return made[(name, dtype)]
+    return get
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("n_live", [20, 64])
+def test_many_live_sequences(wide_engines, oracle, name, dtype, n_live):
+    """20 and 64 sequences of unequal lengths alive at once (the captured steps of 32
+    and 64 rows, the wider tiles of the decode product, decode attention over many
+    sequences), the shorter ones ending earlier, two batches in a row so that every
+    slot and page is used again."""
+    import random
+    eng = wide_engines(name, dtype)
+    V = TINY[name]["vocab_size"]
+    rng = random.Random(n_live)
+    for b in range(2):
+        plan = [(rng.choice([1, 2, 7, 30, 63, 64, 65]), rng.randint(1, 9)) for _ in range(n_live)]
+        plan[rng.randrange(n_live)] = (40, 14)               # one that outlives the others
+        reqs = [random_tokens(p + d, V, 5000 + 100 * b + i) for i, (p, d) in enumerate(plan)]
+        got = run_batch(eng, reqs, [p for p, _ in plan])
+        for i, r in enumerate(reqs):
+            assert_close(got[i], oracle(name, r), dtype, f"{name} {n_live} live, batch {b}, request {i}")
+        eng.cache.check()
+        assert eng.cache.slots.n_held == 0 and eng.cache.tokens_held() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_captured_steps_against_steps_launched_one_by_one(model_dirs, oracle, dtype):
+    """Prompt steps and decode steps through captured graphs (padded to their buckets
+    of tokens, sequences and wanted rows) against the same steps launched kernel by
+    kernel: bit-equal in 32-bit, where no kernel's order of sums depends on the number
+    of rows, and both within the bar of the plain implementation in bfloat16.  And the
+    logits a step returns are the caller's: a later step does not change them."""
+    from grout_b200.engine import Engine
+    lengths, schedule = _mixed_schedule()
+    reqs = [random_tokens(n, TINY["D"]["vocab_size"], 740 + i) for i, n in enumerate(lengths)]
+    outs = {}
+    for use in (True, False):
+        eng = Engine.load(model_dirs["D"], dtype=dtype, max_tokens=2048, max_batch=8,
+                          max_seq_len=512, use_graphs=use)
+        outs[use] = run_schedule(eng, reqs, schedule)
+        if use:
+            assert eng.graphs.prompt_graphs and eng.graphs.decode_graphs
+            s = eng.open_sequence()
+            first = eng.step([(s, reqs[0][:7])], [[6]])
+            kept = first.clone()
+            second = eng.step([(s, reqs[0][7:8])], [[0]])
+            third = eng.step([(s, reqs[0][8:9])], [[0]])
+            kept2 = second.clone()
+            eng.step([(s, reqs[0][9:16])], [[6]])
+            assert torch.equal(first, kept) and torch.equal(second, kept2)
+            assert first.data_ptr() != second.data_ptr() != third.data_ptr()
+            eng.close_sequence(s)
+        else:
+            assert not eng.graphs.prompt_graphs and not eng.graphs.decode_graphs
+        eng.check()
+    for i, r in enumerate(reqs):
+        assert_close(outs[True][i], oracle("D", r), dtype, f"captured, request {i}")
+        assert_close(outs[False][i], oracle("D", r), dtype, f"launched one by one, request {i}")
+        if dtype == "float32":
+            assert torch.equal(outs[True][i], outs[False][i]), i
 
 
 def test_fp32_cuts_agree_tightly(engines):
