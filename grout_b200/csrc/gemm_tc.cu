@@ -784,3 +784,42 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   }
   return GB_ERR_UNSUPPORTED;
 }
+
+// The way a role of the kernels above gives up, run by itself with nothing in
+// flight: no copy is issued, no tensor memory is held, no other block exists.
+// Thread 0 waits, for at most limit_ns, on a barrier at which nobody arrives;
+// when the time is up it records its code in *error and raises the block's
+// abort flag.  Warp 1 waits on a second such barrier with the kernels' own long
+// limit and the abort flag, which is what ends its wait.  The block then leaves
+// like any other.  It exists so that a test can see the whole path (wait, code,
+// abort, return, the host's check) without making a product kernel wait.
+__global__ void tc_wait_selftest_kernel(int* error, unsigned long long limit_ns, int* left) {
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ int abort_s;
+  volatile int* abort_flag = &abort_s;
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    if (!mbar_wait(&bars[0], 0, abort_flag, limit_ns)) {
+      if (!*abort_flag) atomicCAS(error, 0, GB_ERR_TIMEOUT_FULL);
+      *abort_flag = 1;
+    }
+  } else if (warp == 1) {
+    const bool ok = mbar_wait_warp(&bars[1], 0, abort_flag);
+    if (!ok && (threadIdx.x & 31) == 0) atomicAdd(left, 1);   // left because of the abort flag
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) atomicAdd(left, 1);
+}
+// left: device int that the kernel raises by 2 when both roles have left.
+GB_EXPORT int gb_tc_wait_selftest(int* error, long long limit_ns, int* left, cudaStream_t s) {
+  if (!error || !left || limit_ns <= 0 || limit_ns > 1000000000ll) return GB_ERR_BAD_ARG;
+  tc_wait_selftest_kernel<<<1, 64, 0, s>>>(error, (unsigned long long)limit_ns, left);
+  return (int)cudaGetLastError();
+}

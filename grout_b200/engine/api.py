@@ -299,7 +299,9 @@ class Engine:
         are served in batches of unequal prompts; tokens come back as host ints.
         ``look_ahead`` (with ``device_argmax``): queue each decode step before the
         tokens of the one before have been read, its input taken on the device; the
-        tokens returned are the same."""
+        tokens returned are the same in the 32-bit path and, in bfloat16, the same
+        up to the rounding of a step that ran in another bucket of rows
+        (``engine.generate`` says when)."""
         sampling = (sampling or SamplingParams()).normalised()
         if ignore_eos:
             stops: Tuple[int, ...] = ()               # src/model.rs:1517-1521

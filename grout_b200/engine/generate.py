@@ -21,7 +21,12 @@ tokens of this one, and read the tokens while it runs.  Who goes on is then
 decided before the tokens are known: a request that has budget left takes part
 in the next step, and if its token turns out to be a stop token that step was
 run for nothing for its row (its slot is given back as usual, and nothing of the
-row is returned).  The tokens that come back are the same either way.
+row is returned).  In the 32-bit path the tokens that come back are the same
+either way: no kernel's order of sums depends on how many rows a step has.  In
+bfloat16 the row that ran for nothing can put that step into the next bucket of
+rows (17 rows instead of 16), whose products cut their sums differently; the
+other rows' logits then differ by rounding, and a near-tie between two tokens
+may fall the other way.
 """
 from __future__ import annotations
 

@@ -7,6 +7,7 @@ tensor that is not on the GPU, or a size a kernel does not take, raises.
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional, Tuple
 
@@ -46,6 +47,130 @@ def launch_count() -> int:
     """Kernel launches made through this module so far (a decode-attention call
     with more than one split counts its merge kernel too)."""
     return _LAUNCHES
+
+
+class OpProfile:
+    """Per-operation device times of steps that are launched one by one (not
+    replayed from a graph): CUDA events around every call of this module, with
+    the bytes each call has to move and the flops it has to do, so that the
+    report can set every kernel against the machine's peaks.  (The reference's
+    per-op totals: src/model.rs:1139-1142, 1183-1207, filled at 4370-4379.)"""
+
+    def __init__(self, hbm_gbs: Optional[float] = None, tflops: Optional[float] = None):
+        self.hbm_gbs, self.tflops = hbm_gbs, tflops
+        self.records = []          # (name, start event, end event, bytes, flops); the last two may be callables
+
+    def add(self, name, a, b, nbytes, flops) -> None:
+        self.records.append((name, a, b, nbytes, flops))
+
+    def totals(self):
+        """name -> [calls, ms, bytes, flops], after waiting for the device."""
+        torch.cuda.synchronize()
+        out = {}
+        for name, a, b, nbytes, flops in self.records:
+            r = out.setdefault(name, [0, 0.0, 0.0, 0.0])
+            r[0] += 1
+            r[1] += a.elapsed_time(b)
+            r[2] += float(nbytes() if callable(nbytes) else nbytes)
+            r[3] += float(flops() if callable(flops) else flops)
+        return out
+
+    def report(self) -> str:
+        rows = sorted(self.totals().items(), key=lambda kv: -kv[1][1])
+        whole = sum(r[1] for _n, r in rows) or 1.0
+        head = "op profile (an event pair around every call; steps are not replayed from graphs)\n"
+        head += f"  {'op':<22}{'calls':>7}{'total_ms':>10}{'avg_us':>9}{'share':>7}{'GB/s':>9}{'TFLOP/s':>9}"
+        if self.hbm_gbs or self.tflops:
+            head += f"{'of hbm':>8}{'of mma':>8}"
+        lines = [head]
+        for name, (calls, ms, nbytes, flops) in rows:
+            gbs = nbytes / (ms * 1e-3) / 1e9 if ms > 0 else 0.0
+            tfs = flops / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
+            line = (f"  {name:<22}{calls:>7}{ms:>10.3f}{ms / calls * 1e3:>9.2f}{ms / whole:>7.1%}"
+                    f"{gbs:>9.0f}{tfs:>9.1f}")
+            if self.hbm_gbs or self.tflops:
+                line += f"{(gbs / self.hbm_gbs if self.hbm_gbs else 0):>8.2f}"
+                line += f"{(tfs / self.tflops if self.tflops else 0):>8.2f}"
+            lines.append(line)
+        return "\n".join(lines)
+
+
+_PROFILE: Optional[OpProfile] = None
+
+
+def set_profile(profile: Optional[OpProfile]) -> None:
+    """Turns the per-operation profile on (an ``OpProfile``) or off (None)."""
+    global _PROFILE
+    _PROFILE = profile
+
+
+def _nbytes(*tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if isinstance(t, torch.Tensor))
+
+
+def _profiled(name: str, cost):
+    """Decorator: with a profile on, brackets the call with events and notes
+    ``cost(result, *args, **kw) -> (bytes, flops)``."""
+    def deco(fn):
+        @functools.wraps(fn)
+        def wrapper(*args, **kw):
+            prof = _PROFILE
+            if prof is None:
+                return fn(*args, **kw)
+            a = torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = fn(*args, **kw)
+            b = torch.cuda.Event(enable_timing=True)
+            b.record()
+            nbytes, flops = cost(out, *args, **kw)
+            prof.add(name, a, b, nbytes, flops)
+            return out
+        return wrapper
+    return deco
+
+
+def _cost_io(out, *args, **kw):
+    """What goes in and what comes out, each once."""
+    outs = out if isinstance(out, (tuple, list)) else (out,)
+    return _nbytes(*args, *kw.values(), *outs), 0
+
+
+def _cost_gemm(out, x, w, *args, **kw):
+    M, K = x.shape
+    N = w.shape[0]
+    return _nbytes(x, w, out), 2.0 * M * N * K
+
+
+def _cost_attention(out, q, k_pages, *args, **kw):
+    """Keys and values of the live sequences once, q in, the result out; flops of
+    the two products over the keys every query row sees (lengths are on the
+    device: they are read when the report is made)."""
+    nq, D = q.shape[1], q.shape[2]
+    nkv, item = k_pages.shape[1], k_pages.element_size()
+    kv_len, slots, cu_q, window = kw.get("kv_len"), kw.get("slots"), kw.get("cu_q"), kw.get("window")
+    if kv_len is None:
+        return _nbytes(q, out), 0
+    live = (slots >= 0)
+    lens = torch.where(live, kv_len, torch.zeros_like(kv_len)).double()
+    if cu_q is not None:
+        rows = torch.where(live, cu_q[1:] - cu_q[:-1], torch.zeros_like(kv_len)).double()
+    else:
+        rows = live.double()
+    pairs = rows * (lens - rows) + rows * (rows + 1) / 2        # (query, visible key) pairs, causal
+    if window:
+        pairs = torch.minimum(pairs, rows * float(window))
+        lens = torch.minimum(lens, rows + float(window))
+    kv_bytes = (lens.sum() * (2 * nkv * D * item))
+    pair_sum = pairs.sum()
+    base = _nbytes(q, out)
+    return (lambda: base + float(kv_bytes.item())), (lambda: 4.0 * nq * D * float(pair_sum.item()))
+
+
+def _cost_qk_prepare(out, qkv, nq, nkv, D):
+    """The projection in, q out, and k and v out (to their pages or to a tensor)."""
+    q = out[0]
+    kv_bytes = q.shape[0] * 2 * nkv * D * q.element_size()
+    return _nbytes(qkv, q) + kv_bytes, 0
 
 
 def _check(rc: int, what: str, kernels: int = 1) -> None:
@@ -95,6 +220,7 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 # ---------------------------------------------------------------- embedding
+@_profiled("embed", lambda out, table, ids: (_nbytes(ids, out, out), 0))
 def embed(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     _need(table, "embedding table", ndim=2)
     _need(ids, "token ids", torch.int32, 1)
@@ -107,6 +233,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------- norm
+@_profiled("add_rmsnorm", _cost_io)
 def add_rmsnorm(res_in: Optional[torch.Tensor], delta: Optional[torch.Tensor],
                 weight: torch.Tensor, eps: float, *, dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None, write_res: bool = True
@@ -168,6 +295,7 @@ class _QkPrepareArgs(ctypes.Structure):
                 ("part_stride", _L)]
 
 
+@_profiled("qk_prepare", lambda out, qkv, nq, nkv, D, **k: _cost_qk_prepare(out, qkv, nq, nkv, D))
 def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=None,
                eps: float = 0.0, inv_freq=None, rot_dim: int = 0, token_seq, token_pos, slots,
                block_table=None, k_pages=None, v_pages=None, page: int = 0,
@@ -228,6 +356,7 @@ def qk_prepare(qkv: torch.Tensor, nq: int, nkv: int, D: int, *, q_w=None, k_w=No
     return q, kv_out
 
 
+@_profiled("kv_write", lambda out, kv, *a, **k: (2 * _nbytes(kv), 0))
 def kv_write(kv: torch.Tensor, nkv: int, D: int, *, token_seq, token_pos, slots, block_table,
              k_pages, v_pages, page: int) -> None:
     _need(kv, "kv rows", ndim=3)
@@ -261,6 +390,7 @@ def _attn_common(q, k_pages, v_pages, block_table, token_seq, token_pos, slots, 
     return T, nq, nkv, D
 
 
+@_profiled("attn_generic", lambda out, q, *a, **k: (_nbytes(q, out), 0))
 def attn_generic(q, k_pages, v_pages, block_table, *, token_seq, token_pos, slots, page: int,
                  scale: float, window: Optional[int] = None) -> torch.Tensor:
     T, nq, nkv, D = _attn_common(q, k_pages, v_pages, block_table, token_seq, token_pos, slots, page)
@@ -275,6 +405,7 @@ def attn_generic(q, k_pages, v_pages, block_table, *, token_seq, token_pos, slot
 
 
 # ---------------------------------------------------------------- matrix products
+@_profiled("gemm_f32", _cost_gemm)
 def gemm_f32(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """a [M, K] . w [N, K]^T in true 32-bit on the CUDA cores."""
     _need(a, "activations", torch.float32, 2)
@@ -290,6 +421,7 @@ def gemm_f32(a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 
 # ---------------------------------------------------------------- elementwise
+@_profiled("silu_mul", _cost_io)
 def silu_mul(gate_up: torch.Tensor, interleave: int = 0) -> torch.Tensor:
     """silu(gate) * up.  ``interleave`` 0: gate in the first half of the columns,
     up in the second; g > 0: groups of g gate columns followed by their g up columns."""
@@ -304,6 +436,7 @@ def silu_mul(gate_up: torch.Tensor, interleave: int = 0) -> torch.Tensor:
     return out
 
 
+@_profiled("cast", lambda out, x, dtype: ((0, 0) if out is x else (_nbytes(x, out), 0)))
 def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     _need(x, "tensor")
     if x.dtype == dtype:
@@ -316,6 +449,18 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     _check(_fn("elementwise", pair, "pplp")(x.data_ptr(), out.data_ptr(), x.numel(), _stream()),
            "cast")
     return out
+
+
+@_profiled("library_mm", _cost_gemm)
+def library_mm(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """x [M, K] . w [N, K]^T by the library's matrix product (cuBLAS through
+    torch.mm): the prompt products for which the reference calls a library too
+    (src/cublas.rs:287-307).  It is here so that the profile sees it."""
+    _need(x, "activations", torch.bfloat16, 2)
+    _need(w, "weight", torch.bfloat16, 2)
+    if out_dtype == torch.float32:
+        return torch.mm(x, w.t(), out_dtype=torch.float32)
+    return torch.mm(x, w.t())
 
 
 SKINNY_MAX_ROWS = 64
@@ -366,6 +511,7 @@ def skinny_plan(M: int, N: int, K: int, out_f32: bool, silu: bool):
     return plan
 
 
+@_profiled("gemm_skinny_bf16", _cost_gemm)
 def gemm_skinny_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                      silu_mul: bool = False) -> torch.Tensor:
     """x [M <= 64, K] . w [N, K]^T, bf16 in, 32-bit accumulate; the decode-time
@@ -439,6 +585,22 @@ def check_kernel_errors() -> None:
             raise KernelError(f"tensor-memory kernel on cuda:{i}: {_TC_ERROR_NAMES.get(code, code)}")
 
 
+def tc_wait_selftest(device, limit_us: int = 1000) -> int:
+    """Runs the give-up path of the tensor-memory kernels by itself: one block
+    whose first role waits ``limit_us`` on a barrier nobody arrives at, records its
+    code in the device's error flag and raises the block's abort flag, which ends
+    the second role's (long) wait.  Nothing is in flight and nothing else waits.
+    Returns how many roles left (2); ``check_kernel_errors`` then raises."""
+    dev = torch.device(device)
+    left = torch.zeros(1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _check(_fn("gemm_tc", "gb_tc_wait_selftest", "plpp")(
+            _tc_error_flag(dev).data_ptr(), int(limit_us) * 1000, left.data_ptr(), _stream()),
+            "tc_wait_selftest")
+    return int(left.item())
+
+
+@_profiled("gemm_tc_bf16", _cost_gemm)
 def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                  swap: Optional[bool] = None, silu_mul: bool = False,
                  stamps: Optional[torch.Tensor] = None, split_out: bool = False) -> torch.Tensor:
@@ -518,6 +680,7 @@ def gemm_tc2_rounds(M: int, N: int, device) -> float:
     return tiles / max(1, _sm_count(device) // 2)
 
 
+@_profiled("gemm_tc2_bf16", _cost_gemm)
 def gemm_tc2_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                   silu_mul: bool = False, tile_cols: int = 0) -> torch.Tensor:
     """x [M, K] . w [N, K]^T for many rows on pairs of SMs (tcgen05.mma.cta_group::2,
@@ -600,6 +763,7 @@ def _q_blocks(q_lens, n_qblocks, rows: int, T: int, n_seqs: int) -> int:
     return int(n_qblocks)
 
 
+@_profiled("attn_prefill_bf16", _cost_attention)
 def attn_prefill_bf16(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens=(),
                       page: int, scale: float, window: Optional[int] = None,
                       n_qblocks: Optional[int] = None) -> torch.Tensor:
@@ -655,6 +819,7 @@ def attn_prefill_tc_takes(D: int, nq: int, nkv: int, page: int) -> bool:
     return D in (64, 128) and page == 64 and nq % nkv == 0
 
 
+@_profiled("attn_prefill_tc", _cost_attention)
 def attn_prefill_tc(q, k_pages, v_pages, block_table, *, cu_q, slots, kv_len, q_lens=(),
                     page: int, scale: float, window: Optional[int] = None,
                     rows_per_block: int = 0, n_qblocks: Optional[int] = None) -> torch.Tensor:
@@ -712,6 +877,7 @@ def decode_splits(n_seqs: int, nkv: int, max_kv_len: int, device) -> int:
     return min(s for s, c in cost.items() if c <= 1.03 * best)
 
 
+@_profiled("attn_decode_bf16", _cost_attention)
 def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: int, scale: float,
                      max_kv_len: int, window: Optional[int] = None,
                      n_splits: Optional[int] = None) -> torch.Tensor:
@@ -774,6 +940,7 @@ def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float
 
 
 # ---------------------------------------------------------------- sampling
+@_profiled("argmax", lambda out, logits: (_nbytes(logits), 0))
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     """First maximum of every row of 32-bit logits -> int32 [rows]."""
     _need(logits, "logits", torch.float32, 2)
@@ -785,6 +952,7 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     return out
 
 
+@_profiled("sample", lambda out, logits, *a: (_nbytes(logits), 0))
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
            top_p: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
     """One token per row from temperature / top-k / top-p sampling with the

@@ -75,9 +75,7 @@ class Linear:
                     (self.prefill_kernel == "auto" and
                      ops.gemm_tc2_rounds(M, self.out_features, x.device) >= 2.0)):
                 return ops.gemm_tc2_bf16(x, w, out_dtype)
-        if out_dtype == torch.float32:
-            return torch.mm(x, w.t(), out_dtype=torch.float32)
-        return torch.mm(x, w.t())
+        return ops.library_mm(x, w, out_dtype)
 
     def silu_mul(self, x: torch.Tensor, interleave: int) -> torch.Tensor:
         """silu(gate) * up of a fused gate|up weight.  ``interleave`` 0: gate rows

@@ -134,16 +134,52 @@ def test_limits(model_dirs):
         eng.step([(eng.open_sequence(), [256])])
 
 
+def test_looking_ahead_across_a_bucket_of_rows(model_dirs):
+    """17 requests of which one draws a stop token early: stepping in turn, the step
+    after it has 16 rows; looking ahead, the request still holds a row there and the
+    step has 17, which is the next bucket of the captured steps.  The 32-bit path gives
+    the same tokens either way; the bfloat16 path, where the wider bucket's products
+    round differently, is held to the same finish reasons."""
+    from grout_b200.engine import Engine
+    from grout_b200.engine.generate import Request
+    from grout_b200.sampling import SamplingParams
+    prompts = [random_tokens(3 + i, 384, 1760 + i) for i in range(17)]
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.load(model_dirs["B"], dtype=dtype, max_tokens=32 * 64, max_batch=32,
+                          max_seq_len=64, use_graphs=True)
+        free = eng.generate(prompts, 8, ignore_eos=True, look_ahead=False)
+        stop = free[5].token_ids[2]
+        reqs = [Request(p, 8, SamplingParams().normalised(), (stop,)) for p in prompts]
+        in_turn = eng.generate(reqs, look_ahead=False)
+        ahead = eng.generate(reqs, look_ahead=True)
+        assert in_turn[5].finish_reason == "stop" and len(in_turn[5].token_ids) <= 2
+        assert {16, 32} <= {b for b, _l in eng.graphs.decode_graphs}
+        if dtype == "float32":
+            assert [o.token_ids for o in ahead] == [o.token_ids for o in in_turn]
+        assert [o.finish_reason for o in ahead] == [o.finish_reason for o in in_turn]
+        eng.cache.check()
+
+
 def test_a_kernel_that_gave_up_on_a_wait_is_reported(model_dirs):
-    """The tensor-memory kernels bound their waits and record a code in a device flag when
-    one runs out.  Generation reads the flag after every batch and raises; here the flag is
-    set by hand (no kernel is made to wait), and the next call is clean again."""
+    """The tensor-memory kernels bound their waits; when one runs out the role records
+    a code in a device flag, raises its block's abort flag (which ends the waits of the
+    block's other roles) and the block leaves.  A kernel made for this test walks that
+    path by itself: one block, a barrier at which nobody arrives, a limit of one
+    millisecond, nothing in flight.  ``Engine.check`` and generation then raise, the
+    batch's slots come back all the same, and the next call is clean again."""
+    import time
     from grout_b200.engine import Engine
     from grout_b200.kernels import ops
     eng = Engine.load(model_dirs["A"], dtype="bfloat16", max_tokens=1024, max_batch=4, max_seq_len=128)
     prompts = [random_tokens(9, TINY["A"]["vocab_size"], 77)]
     good = eng.generate(prompts, max_new_tokens=4, ignore_eos=True)
-    ops._tc_error_flag(torch.device("cuda:0")).fill_(101)
+    t0 = time.time()
+    assert ops.tc_wait_selftest(eng.device, limit_us=1000) == 2      # both roles left
+    assert time.time() - t0 < 1.0                # the second role did not sit out its own 2 s
+    with pytest.raises(ops.KernelError, match="stage that never arrived"):
+        eng.check()
+    eng.check()                                  # the flag was cleared by the report
+    ops.tc_wait_selftest(eng.device, limit_us=1000)
     with pytest.raises(ops.KernelError, match="stage that never arrived"):
         eng.generate(prompts, max_new_tokens=4, ignore_eos=True)
     eng.cache.check()

@@ -548,6 +548,89 @@ def test_attn_prefill_tc(nq, nkv, D, window, rows_per_block):
         assert torch.allclose(got[cu[4] + 299, 0].double(), pc.v[4][3, 0].double(), atol=1e-2, rtol=1e-2)
 
 
+def _plant_window_edge(q, row, pc, seq, pos, window):
+    """Makes query ``row`` (at position ``pos`` of sequence ``seq``) look along one
+    axis only, and gives two keys a component there: the key just outside its
+    window (pos - window) the largest, the key just inside (pos - window + 1) the
+    second largest, every other key of the sequence none.  With the window right
+    the output is the inner key's value; one key too many and it is the outer
+    key's value; one too few and it is a blend of all of them."""
+    q[row] = 0
+    q[row, :, 0] = 30.0
+    pc.k[seq][pos - window, :, 0] = 30.0
+    pc.k[seq][pos - window + 1, :, 0] = 20.0
+
+
+def _clear_axis(pc, seq):
+    pc.k[seq][:, :, 0] = 0
+
+
+def _restore(pc, seq):
+    for j in range(pc.k[seq].shape[0]):
+        pc.store(seq, j, pc.k[seq][j], pc.v[seq][j])
+
+
+@pytest.mark.parametrize("kernel", ["decode-1", "decode-3", "mma", "tc-128", "tc-256"])
+@pytest.mark.parametrize("nq,nkv,D", [(8, 2, 128), (6, 3, 64)])
+def test_the_window_edge_to_the_key(kernel, nq, nkv, D):
+    """The tensor-core attention kernels at a window's edge, with keys planted so that
+    an edge off by one in either direction changes the output entirely: edges that fall
+    on a page boundary (the outer key the last of page 0, the inner the first of
+    page 1), inside a page, and in a continued prompt."""
+    ops = _ops()
+    dt, W = torch.bfloat16, 70
+    scale = 1.0 / math.sqrt(D)
+    if kernel.startswith("decode"):
+        # the one query of each sequence sits at its last position
+        lens = [W + 64, W + 81, 3 * 64 + 5, W + 1]
+        pc = Paged(lens, nkv, D, dt, 60)
+        q = _rand((len(lens), nq, D), dt, 61)
+        planted = []
+        for s, n in enumerate(lens):
+            _clear_axis(pc, s)
+            _plant_window_edge(q, s, pc, s, n - 1, W)
+            _restore(pc, s)
+            planted.append((s, s, n - 1))
+        got = ops.attn_decode_bf16(
+            q.to(DEV), pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV),
+            slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
+            kv_len=torch.tensor(lens, dtype=torch.int32, device=DEV), page=64, scale=scale,
+            max_kv_len=512, window=W, n_splits=int(kernel[-1])).cpu()
+    else:
+        # (tokens already held, tokens of this step); planted rows by position
+        plan = [(0, 260), (50, 200)]
+        spots = {0: [63 + W, 210], 1: [63 + W, 249]}
+        lens = [a + n for a, n in plan]
+        pc = Paged(lens, nkv, D, dt, 62, fill=300.0)
+        cu = [0, plan[0][1], plan[0][1] + plan[1][1]]
+        q = _rand((cu[-1], nq, D), dt, 63)
+        planted = []
+        for s, (held, n) in enumerate(plan):
+            _clear_axis(pc, s)
+            for pos in spots[s]:
+                _plant_window_edge(q, cu[s] + pos - held, pc, s, pos, W)
+                planted.append((cu[s] + pos - held, s, pos))
+            _restore(pc, s)
+        common = dict(cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                      slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
+                      kv_len=torch.tensor(lens, dtype=torch.int32, device=DEV),
+                      q_lens=tuple(n for _, n in plan), page=64, scale=scale, window=W)
+        args = (q.to(DEV), pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV))
+        if kernel == "mma":
+            got = ops.attn_prefill_bf16(*args, **common).cpu()
+        else:
+            got = ops.attn_prefill_tc(*args, rows_per_block=int(kernel[3:]), **common).cpu()
+            ops.check_kernel_errors()
+    g = nq // nkv
+    for row, s, pos in planted:
+        for h in range(nq):
+            inner = pc.v[s][pos - W + 1, h // g].double()
+            outer = pc.v[s][pos - W, h // g].double()
+            assert torch.allclose(got[row, h].double(), inner, atol=1e-2, rtol=1e-2), \
+                (kernel, row, s, pos, h, "outer key seen" if torch.allclose(
+                    got[row, h].double(), outer, atol=1e-2, rtol=1e-2) else "inner key missed")
+
+
 @pytest.mark.parametrize("N", [200, 2560])
 def test_add_rmsnorm_takes_partial_sums(N):
     """The residual add accepts the 32-bit partial sums of a split-K product."""

@@ -1,5 +1,6 @@
 """bin/trace_run driven as a user would: the same requests whole, with the last
-32 tokens one by one, and in batches of unequal lengths, in both precisions."""
+32 tokens one by one, in batches of unequal lengths, in chunks, and in steps that
+mix one and several tokens, in both precisions."""
 import json
 import os
 import subprocess
@@ -55,6 +56,17 @@ def _trace():
     reqs["s0"], reqs["s1"] = random_tokens(65, V, 820), random_tokens(3, V, 821)
     add([("s0", 0, 64, True), ("s1", 0, 2, True)])
     add([("s0", 64, 65, True), ("s1", 2, 3, True)], end=["s0", "s1"])
+    # a prompt fed in pieces that end one short of a page, on it and beyond it
+    reqs["c0"] = random_tokens(140, V, 830)
+    o = 0
+    for n in (63, 1, 64, 12):
+        add([("c0", o, o + n, True)], end=["c0"] if o + n == 140 else [])
+        o += n
+    # steps that mix one and several tokens, and a request that starts while others go on
+    reqs["m0"], reqs["m1"], reqs["m2"] = (random_tokens(n, V, 840 + n) for n in (26, 11, 71))
+    add([("m0", 0, 20, True), ("m1", 0, 9, False)])
+    add([("m0", 20, 25, True), ("m1", 9, 10, True), ("m2", 0, 70, True)])
+    add([("m0", 25, 26, True), ("m1", 10, 11, True), ("m2", 70, 71, True)], end=["m0", "m1", "m2"])
     return reqs, steps, rows
 
 
