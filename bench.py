@@ -6,11 +6,21 @@ random weights on one B200.
 
 A "step" is one decode step of the whole batch (default 8 sequences that each
 hold a 2,048-token prompt, context 4096).  ``value`` is decoded tokens per
-second timed on the device with CUDA events over exactly K steps; ``e2e`` is
-the same through ``Engine.generate`` with host token lists in and out.  The
-line also carries the 2,048-token prefill, the decode step's HBM roofline and
-decode at batch 1 and 64.  Every decode step reads the 8 GB of weights, far more
-than the 126 MB L2, so nothing is flushed between timed steps.
+second timed on the device with CUDA events over exactly K steps; ``regions``
+cuts the same K steps into five consecutive regions (an event between them) and
+gives the median and the quartiles of their times per step, in the manner of
+the reference's repetitions (benchmarks/src/bin/grout_bench.rs:218-252);
+``e2e`` is the same through ``Engine.generate`` with host token lists in and
+out.  The line also carries the 2,048-token prefill, the decode step's HBM
+roofline and decode at batch 1 and 64.  Every decode step reads the 8 GB of
+weights, far more than the 126 MB L2, so nothing is flushed between timed steps.
+
+    python bench.py --size 8b|32b      the same run at the other sizes of the workload list
+    python bench.py --ops [--size S] [--batch B]
+                                       a table of every kernel of one prompt step and of
+                                       decode steps (launched one by one, an event pair
+                                       around each): calls, time, GB/s, TFLOP/s, fractions
+    python bench.py --requests S       the reference's request grid
 """
 import argparse
 import json
@@ -29,7 +39,6 @@ QWEN3_4B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_si
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, rope_theta=1000000.0,
                 rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=True,
                 use_sliding_window=False, eos_token_id=151645)
-FULL_LAYERS = 36
 # The other two model sizes of the workload list, for --requests (layer sizes only; the
 # default run and its contract stay with the 4B sizes).
 SIZES = {
@@ -46,7 +55,9 @@ PUBLISHED_32B = {(18, 36): 79.6, (18, 128): 79.9, (18, 512): 80.1, (128, 36): 79
 PUBLISHED_32B_PREFILL_MS = {8192: 513.78}
 CONTEXT = 4096
 PROMPT = 2048
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+SETTLE_S = 0.5      # idle between a batch's prompts and its decode steps (see decode_run)
+REGIONS = 5
 
 
 def peaks():
@@ -56,6 +67,7 @@ def peaks():
             with open(path) as fh:
                 p = json.load(fh)
             return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
                     "source": "measured"}
         except Exception:
             pass
@@ -157,6 +169,56 @@ def run_requests(size: str, reps: int) -> int:
     return 0
 
 
+def quartiles(xs):
+    xs = sorted(xs)
+    q = statistics.quantiles(xs, n=4, method="inclusive") if len(xs) > 1 else [xs[0]] * 3
+    return q[0], q[1], q[2]
+
+
+def run_ops(size: str, batch: int, layers: int, pk) -> int:
+    """One prompt step of 2,048 tokens and four decode steps of ``batch`` sequences,
+    launched kernel by kernel with an event pair around each: the table of
+    ``ops.OpProfile`` for each phase.  The times are those of kernels that run alone,
+    one after the other; inside a captured step they overlap at their edges."""
+    import torch
+    from grout_b200.engine import Engine
+    from grout_b200.kernels import ops
+    cfg = dict(SIZES[size], num_hidden_layers=layers)
+    eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=batch * (PROMPT + 128),
+                        max_batch=batch, max_seq_len=CONTEXT, use_graphs=False)
+    g = torch.Generator().manual_seed(1)
+    V = cfg["vocab_size"]
+
+    def prompt():
+        return torch.randint(0, V, (PROMPT,), generator=g).tolist()
+
+    slots = [eng.open_sequence() for _ in range(batch)]
+    eng.step([(slots[0], prompt())], [[PROMPT - 1]])                  # warm-up of every prompt kernel
+    eng.close_sequence(slots[0])
+    slots[0] = eng.open_sequence()
+    prof = ops.OpProfile(pk["hbm_gbs"], pk["bf16_tflops"])
+    ops.set_profile(prof)
+    eng.step([(slots[0], prompt())], [[PROMPT - 1]])
+    ops.set_profile(None)
+    print(f"== prompt step, {PROMPT} tokens, Qwen3-{size.upper()} layer sizes, {layers} layers "
+          f"(peaks: {pk['source']}, {pk['hbm_gbs']:.0f} GB/s, {pk['bf16_tflops']:.0f} TFLOP/s burst)")
+    print(prof.report())
+    for i in range(1, batch, 8):
+        eng.step([(s, prompt()) for s in slots[i:i + 8]])
+    tok = torch.randint(0, V, (batch,), generator=g).tolist()
+    for _ in range(2):
+        eng.step([(s, [t]) for s, t in zip(slots, tok)], [[0]] * batch)
+    prof = ops.OpProfile(pk["hbm_gbs"], pk["bf16_tflops"])
+    ops.set_profile(prof)
+    for _ in range(4):
+        eng.step([(s, [t]) for s, t in zip(slots, tok)], [[0]] * batch)
+    ops.set_profile(None)
+    print(f"== 4 decode steps, batch {batch}, {PROMPT + 3}-{PROMPT + 6} keys a sequence")
+    print(prof.report())
+    eng.check()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -164,14 +226,19 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS,
-                    help="fewer layers than the configuration's 36 (both numbers are reported)")
+    ap.add_argument("--size", default="4b", choices=sorted(SIZES),
+                    help="layer sizes of the run (default: the 4B sizes the contract names)")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--phases", default="prefill,decode,points,e2e",
                     help="which measurements to run (a profiler wants one at a time)")
     ap.add_argument("--requests", default=None, choices=sorted(SIZES),
                     help="instead of the default run: the reference's request grid at this model size")
     ap.add_argument("--reps", type=int, default=5, help="measured requests per cell of --requests")
+    ap.add_argument("--ops", action="store_true",
+                    help="instead of the default run: the per-kernel table of a prompt step and of "
+                         "decode steps at --size and --batch")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -184,6 +251,11 @@ def main() -> int:
         return 2
     if args.requests:
         return run_requests(args.requests, max(1, args.reps))
+    full_layers = SIZES[args.size]["num_hidden_layers"]
+    layers = args.layers or full_layers
+    pk = peaks()
+    if args.ops:
+        return run_ops(args.size, args.batch, layers, pk)
     W = max(args.warmup, 3)
     K = args.steps
     most = CONTEXT - PROMPT - W - 4      # the sequences hold 2,048 prompt tokens in a context of 4,096
@@ -199,8 +271,7 @@ def main() -> int:
     from grout_b200.engine import Engine
     from grout_b200.kernels import ops
 
-    cfg = dict(QWEN3_4B, num_hidden_layers=args.layers)
-    pk = peaks()
+    cfg = dict(SIZES[args.size], num_hidden_layers=layers)
     torch.manual_seed(0)
     biggest = max(args.batch, 64 if "points" in phases else 1)
     room = PROMPT + W + K + 64
@@ -232,10 +303,14 @@ def main() -> int:
     prefill = None
     if times:
         pre_ms = statistics.median(times)
-        pre_flops = prefill_flops(cfg, args.layers, PROMPT)
+        rate = prefill_flops(cfg, layers, PROMPT) / (pre_ms * 1e-3) / 1e12
+        # the step's flops / time / the peak of its dtype: against the burst peak (a product
+        # timed alone) and against the sustained one (nine prompt steps back to back run at
+        # the clocks of the power cap, as that peak was taken)
         prefill = {"value": round(PROMPT / pre_ms * 1e3, 1), "tokens": PROMPT, "ms": round(pre_ms, 3),
-                   "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
-                   "of": pk["source"]}
+                   "frac": round(rate / pk["bf16_tflops"], 4),
+                   "frac_sustained": round(rate / pk["bf16_tflops_sustained"], 4),
+                   "tflops": round(rate, 1), "of": pk["source"]}
 
     # ---- decode --------------------------------------------------------------------
     def decode_run(batch, steps, warm, sample_clocks=False):
@@ -246,6 +321,12 @@ def main() -> int:
         # feed the next step, which is queued without waiting for the host
         first = torch.randint(0, V, (batch,), generator=g).tolist()
         logits = eng.step([(s, [first[j]]) for j, s in enumerate(slots)], [[0]] * batch)
+        # The prompts leave the GPU at the reduced clocks of its power cap, and it raises
+        # them again over some thirty decode steps; the decode step is measured at the
+        # clocks it settles at, so the GPU idles for half a second first.  (``e2e`` below
+        # has no such pause: it is the request as a user runs it.)
+        torch.cuda.synchronize()
+        time.sleep(SETTLE_S)
         greedy = [eng.default_sampling()] * batch
         entries = [(s, j) for j, s in enumerate(slots)]
         for i in range(warm):
@@ -255,13 +336,21 @@ def main() -> int:
         if clocks:
             clocks.start()
         before = ops.launch_count()
-        a, b = ev(), ev()
-        a.record()
+        cuts = sorted({round(steps * r / REGIONS) for r in range(1, REGIONS)} - {0, steps})
+        marks = [ev()]
+        marks[0].record()
         for i in range(steps):
             logits = eng.step_ahead(entries, eng.choose_ahead(logits, greedy, [0.0] * batch))
-        b.record()
+            if i + 1 in cuts:
+                marks.append(ev())
+                marks[-1].record()
+        marks.append(ev())
+        marks[-1].record()
         torch.cuda.synchronize()
-        ms = a.elapsed_time(b)
+        ms = marks[0].elapsed_time(marks[-1])
+        bounds = [0] + cuts + [steps]
+        per_step = [a.elapsed_time(b) / (hi - lo)
+                    for a, b, lo, hi in zip(marks, marks[1:], bounds, bounds[1:])]
         launches = ops.launch_count() - before
         graph = eng.graphs.decode(batch, PROMPT + warm + steps + 1)
         if graph is not None and graph.graph is not None:
@@ -269,20 +358,28 @@ def main() -> int:
         ctx_mid = PROMPT + warm + steps / 2.0
         for s in slots:
             eng.close_sequence(s)
-        return ms, launches, ctx_mid, (clocks.stop() if clocks else None)
+        return ms, launches, ctx_mid, (clocks.stop() if clocks else None), per_step
 
-    ms, launches, ctx_mid, clocks = decode_run(args.batch, K, W, sample_clocks=True)
+    def step_bytes(batch, ctx):
+        return weight_bytes(cfg, layers) + batch * ctx * kv_bytes_per_token(cfg, layers)
+
+    ms, launches, ctx_mid, clocks, per_step = decode_run(args.batch, K, W, sample_clocks=True)
     value = args.batch * K / ms * 1e3
-    step_bytes = weight_bytes(cfg, args.layers) + args.batch * ctx_mid * kv_bytes_per_token(cfg, args.layers)
-    achieved = step_bytes / (ms / K * 1e-3) / 1e9
+    achieved = step_bytes(args.batch, ctx_mid) / (ms / K * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                 "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4), "of": pk["source"]}
+    q1, med, q3 = quartiles(per_step)
+    regions = {"n": len(per_step), "ms_per_step_median": round(med, 4),
+               "ms_per_step_q1": round(q1, 4), "ms_per_step_q3": round(q3, 4),
+               "value_at_median": round(args.batch / med * 1e3, 1)}
 
     points = {}
     if "points" in phases:
         for bsz in (1, 64):
-            m, _l, _c, _ = decode_run(bsz, 32, 4)
+            m, _l, c, _, _p = decode_run(bsz, 32, 4)
             points[f"decode_b{bsz}"] = round(bsz * 32 / m * 1e3, 1)
+            points[f"decode_b{bsz}_hbm_frac"] = round(
+                step_bytes(bsz, c) / (m / 32 * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
 
     # ---- end to end through the Python entry point -----------------------------------
     e2e = None
@@ -298,21 +395,24 @@ def main() -> int:
                "d2h_bytes_per_step": 4 * args.batch}
 
     eng.check()      # a kernel that gave up on a bounded wait would have voided the numbers
+    name = f"Qwen3-{args.size.upper()}"
     print(json.dumps({
-        "metric": f"decode tok/s (Qwen3-4B shape, batch {args.batch}, 2,048-token prompts)",
+        "metric": f"decode tok/s ({name} shape, batch {args.batch}, 2,048-token prompts)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {"model": "Qwen3-4B layer sizes, random weights", "layers": args.layers,
-                   "layers_of_config": FULL_LAYERS, "hidden": cfg["hidden_size"],
+        "config": {"model": f"{name} layer sizes, random weights", "layers": layers,
+                   "layers_of_config": full_layers, "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
                    "vocab": V, "global_batch": args.batch, "seq_len": CONTEXT,
-                   "prompt_len": PROMPT, "tied_head": True, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (8 GB of weights per step), no flush",
-                   "peaks": pk["source"]},
+                   "prompt_len": PROMPT, "tied_head": bool(cfg["tie_word_embeddings"]),
+                   "parallelism": "single GPU",
+                   "l2": f"inputs larger than L2 ({weight_bytes(cfg, layers) / 1e9:.0f} GB of weights "
+                         f"per step), no flush",
+                   "settle_s": SETTLE_S, "peaks": pk["source"]},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "prefill": prefill,
-        "roofline": roofline, "points": points}))
+        "roofline": roofline, "regions": regions, "points": points}))
     return 0
 
 

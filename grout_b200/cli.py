@@ -47,6 +47,14 @@ def build_parser() -> argparse.ArgumentParser:
                     help="choose tokens on the GPU (otherwise logits are copied back and the "
                          "host chooses)")
     ap.add_argument("--profile", action="store_true", help="print step counts and device times")
+    ap.add_argument("--profile-ops", action="store_true",
+                    help="with --profile: time every operation too (calls, time, GB/s, TFLOP/s per "
+                         "kernel).  Steps are then launched kernel by kernel instead of replayed from "
+                         "graphs, so the step times of this run are not the engine's.  The environment "
+                         "variable GROUT_PROFILE_OPS=1 does the same (src/model.rs:1139)")
+    ap.add_argument("--peaks", default=None, metavar="FILE",
+                    help="JSON with hbm_gbs and bf16_tflops: the op profile then gives each kernel's "
+                         "fraction of them")
     ap.add_argument("--warmup-reps", type=int, default=1,
                     help="discarded generations before the measured one")
     ap.add_argument("--ignore-eos", action="store_true", help="generate the whole budget")
@@ -118,8 +126,18 @@ def main(argv: Optional[List[str]] = None) -> int:
 
     for _ in range(args.warmup_reps):          # src/main.rs:101-110
         run(min(args.max_new_tokens, 8))
+    op_profile = None
     if args.profile:
         engine.profile = StepProfile()
+        if args.profile_ops or os.environ.get("GROUT_PROFILE_OPS") == "1":
+            from .kernels import ops
+            peaks = {}
+            if args.peaks:
+                with open(args.peaks, encoding="utf-8") as fh:
+                    peaks = json.load(fh)
+            op_profile = ops.OpProfile(peaks.get("hbm_gbs"), peaks.get("bf16_tflops"))
+            engine.use_graphs = False
+            ops.set_profile(op_profile)
     reps = max(1, args.reps)
     for i in range(reps):                      # benchmarks/src/bin/grout_bench.rs:96-110, 150-190
         out = run(args.max_new_tokens)
@@ -148,6 +166,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     if args.profile and not args.quiet:
         print()
         print(engine.profile.report())
+        if op_profile is not None:
+            print(op_profile.report())
     if args.output_json:
         with open(args.output_json, "w", encoding="utf-8") as fh:
             json.dump({"text": text, "token_ids": out.token_ids, "prompt_tokens": out.prompt_tokens,

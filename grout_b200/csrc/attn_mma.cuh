@@ -52,6 +52,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Where element (row, col) of a key or value tile lies in shared memory.
+// PaddedTile: rows of D + 8 elements, written by 16-byte asynchronous copies.
+// Swizzled128Tile: what TMA writes for boxes of ROWS x 64 elements under the
+// 128-byte swizzle, one box per 64 columns, the boxes one after the other (each
+// box 1024-byte aligned): the 16-byte chunk c of row r sits at chunk c ^ (r % 8).
+// Both keep the eight rows of one ldmatrix phase in eight different bank groups.
+template <int D>
+struct PaddedTile {
+  __device__ __forceinline__ static int off(int row, int col) { return row * (D + 8) + col; }
+};
+template <int ROWS>
+struct Swizzled128Tile {
+  __device__ __forceinline__ static int off(int row, int col) {
+    return (col >> 6) * (ROWS * 64) + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3) + (col & 7);
+  }
+};
+
 // The state of one warp's 16 query rows: this lane holds rows g = lane/4 and
 // g + 8, and of every 8-wide group of columns the pair 2t, 2t+1 (t = lane%4).
 template <int DT>  // head_dim = 16 * DT
@@ -91,9 +108,12 @@ struct WarpAttn {
   // The same with `between()` called once the scores are computed, that is when k_tile has
   // been read for the last time and before v_tile is read for the first: a caller that
   // pipelines its copies refills the key buffer and waits for the values there.
-  template <int NKEYS, bool MASK, typename F>
+  // L says where an element of a tile lies; the NKEYS keys are the tiles' rows row0 ..
+  // row0 + NKEYS - 1 (row0 a multiple of 8).
+  template <int NKEYS, bool MASK, typename L = PaddedTile<16 * DT>, typename F>
   __device__ __forceinline__ void tile(const bf16* k_tile, const bf16* v_tile, int key0,
-                                       const int (&lo)[2], const int (&hi)[2], float c, F&& between) {
+                                       const int (&lo)[2], const int (&hi)[2], float c, F&& between,
+                                       int row0 = 0) {
     const int lane = threadIdx.x & 31, t = lane & 3;
     constexpr int NT = NKEYS / 8;
     float s[NT][4];
@@ -109,7 +129,7 @@ struct WarpAttn {
 #pragma unroll
         for (int j = 0; j < NT; j += 2) {
           uint32_t b[4];
-          ldmatrix_x4(b, k_tile + (j * 8 + krow) * LD + k * 16 + kcol);
+          ldmatrix_x4(b, k_tile + L::off(row0 + j * 8 + krow, k * 16 + kcol));
           mma_16816(s[j], q[k], b[0], b[1]);
           mma_16816(s[j + 1], q[k], b[2], b[3]);
         }
@@ -170,7 +190,7 @@ struct WarpAttn {
 #pragma unroll
       for (int i = 0; i < DT; ++i) {
         uint32_t b[4];
-        ldmatrix_x4_trans(b, v_tile + (kk * 16 + vrow) * LD + i * 16 + vcol);
+        ldmatrix_x4_trans(b, v_tile + L::off(row0 + kk * 16 + vrow, i * 16 + vcol));
         mma_16816(o[2 * i], p, b[0], b[1]);
         mma_16816(o[2 * i + 1], p, b[2], b[3]);
       }

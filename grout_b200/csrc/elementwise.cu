@@ -99,3 +99,24 @@ GB_EXPORT int gb_cast_f32_to_bf16(const void* in, void* out, long long n, cudaSt
 GB_EXPORT int gb_cast_bf16_to_f32(const void* in, void* out, long long n, cudaStream_t s) {
   return cast<bf16, float>(in, out, n, s);
 }
+
+// Keeps the stream busy for `ns` nanoseconds (at most a millisecond): one thread
+// reads the global timer until the time is up and waits for nothing else.  The
+// per-operation profile queues it in front of each timed call so that the host
+// has queued the call and its two events before the device reaches them;
+// otherwise the time between the events of a short kernel is the host's, not
+// the kernel's.
+__global__ void delay_kernel(unsigned long long ns) {
+  unsigned long long t0, t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  for (int i = 0; i < (1 << 20); ++i) {          // bounded whatever the timer does
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    if (t - t0 >= ns) break;
+    __nanosleep(200);
+  }
+}
+GB_EXPORT int gb_delay_ns(long long ns, cudaStream_t s) {
+  if (ns < 0 || ns > 1000000) return GB_ERR_BAD_ARG;
+  delay_kernel<<<1, 1, 0, s>>>((unsigned long long)ns);
+  return gb_status();
+}

@@ -56,8 +56,13 @@ class OpProfile:
     report can set every kernel against the machine's peaks.  (The reference's
     per-op totals: src/model.rs:1139-1142, 1183-1207, filled at 4370-4379.)"""
 
-    def __init__(self, hbm_gbs: Optional[float] = None, tflops: Optional[float] = None):
-        self.hbm_gbs, self.tflops = hbm_gbs, tflops
+    def __init__(self, hbm_gbs: Optional[float] = None, tflops: Optional[float] = None,
+                 lead_us: int = 80):
+        """``lead_us``: how long the device is kept busy in front of every timed
+        call (a timer kernel), so that the call and its events are queued by the
+        time the device gets to them and the interval is the kernel's own; 0
+        for none."""
+        self.hbm_gbs, self.tflops, self.lead_us = hbm_gbs, tflops, int(lead_us)
         self.records = []          # (name, start event, end event, bytes, flops); the last two may be callables
 
     def add(self, name, a, b, nbytes, flops) -> None:
@@ -78,7 +83,8 @@ class OpProfile:
     def report(self) -> str:
         rows = sorted(self.totals().items(), key=lambda kv: -kv[1][1])
         whole = sum(r[1] for _n, r in rows) or 1.0
-        head = "op profile (an event pair around every call; steps are not replayed from graphs)\n"
+        head = ("op profile (an event pair around every call, each kernel alone on the device; steps are "
+                "not replayed from graphs)\n")
         head += f"  {'op':<22}{'calls':>7}{'total_ms':>10}{'avg_us':>9}{'share':>7}{'GB/s':>9}{'TFLOP/s':>9}"
         if self.hbm_gbs or self.tflops:
             head += f"{'of hbm':>8}{'of mma':>8}"
@@ -118,9 +124,11 @@ def _profiled(name: str, cost):
             if prof is None:
                 return fn(*args, **kw)
             a = torch.cuda.Event(enable_timing=True)
+            b = torch.cuda.Event(enable_timing=True)
+            if prof.lead_us:
+                _fn("elementwise", "gb_delay_ns", "lp")(prof.lead_us * 1000, _stream())
             a.record()
             out = fn(*args, **kw)
-            b = torch.cuda.Event(enable_timing=True)
             b.record()
             nbytes, flops = cost(out, *args, **kw)
             prof.add(name, a, b, nbytes, flops)
@@ -733,7 +741,7 @@ class _DecodeArgs(ctypes.Structure):
 _LOG2E = 1.4426950408889634
 PREFILL_ROWS = 64          # query rows per block of the prefill kernel
 FAST_ATTENTION_MODULES: Tuple[str, ...] = ("attn_prefill_tc", "attn_prefill_bf16",
-                                            "attn_decode_bf16")
+                                            "attn_decode_bf16", "attn_decode_tma")
 PREFILL_ATTENTION = "tc"      # "tc": tcgen05 where the shape allows; "mma": the mma.sync kernel
 _SM_COUNT = {}
 
@@ -913,6 +921,98 @@ def attn_decode_bf16(q, k_pages, v_pages, block_table, *, slots, kv_len, page: i
     return out
 
 
+class _DecodeTmaArgs(ctypes.Structure):
+    _fields_ = [("q", _P), ("block_table", _P), ("slots", _P), ("kv_len", _P), ("out", _P),
+                ("part_o", _P), ("part_ml", _P), ("counters", _P), ("error", _P), ("n_seqs", _I),
+                ("nq", _I), ("nkv", _I), ("max_pages", _I), ("window", _I), ("n_splits", _I),
+                ("scale_log2", _F)]
+
+
+_TC_ERROR_NAMES[131] = "a role of the decode attention kernel waited 2 s on a barrier"
+# Which decode attention runs: "auto" takes the TMA kernel where the shape allows and the
+# step has at least DECODE_TMA_PAIRS (sequence, kv head) pairs, and the cp.async kernel for
+# fewer; "tma" and "mma" force one.  Measured inside the decode step at 32 query and 8 kv
+# heads of 128 with 2,100 keys a sequence (ms a step, cp.async / TMA): 64 sequences 6.41 /
+# 5.99, 8 sequences 2.74 / 2.78, one sequence 2.38 / 2.48.  Timed by itself, one call after
+# the other, the TMA kernel is the faster or the equal at every size (16.8 against 17.9 us at
+# 8 sequences, 86 against 97 at 64); inside a step, where a short kernel comes before it, its
+# longer start (descriptor fetch, barrier set-up, the hand-over from the loading lane) shows
+# when there are few blocks to hide it behind.
+DECODE_ATTENTION = "auto"
+DECODE_TMA_PAIRS = 128
+DECODE_TMA_STAGES = 0         # tiles of a block in shared memory (0: the kernel's default)
+_ATTN_COUNTERS = {}
+
+
+def attn_decode_tma_takes(D: int, nq: int, nkv: int, page: int) -> bool:
+    return D in (64, 128) and page == 64 and nq % nkv == 0 and nq // nkv <= 16
+
+
+def decode_tma_splits(n_seqs: int, nkv: int, max_kv_len: int, device, per_sm: int = 2) -> int:
+    """How many ways the keys of a sequence are split for the TMA kernel: blocks
+    run in waves of ``per_sm`` per SM; with S splits a block streams 1/S of a
+    sequence's 64-key tiles plus a fixed cost of about six tiles (descriptor and
+    block-table loads before the first copy, the partial store and the combining
+    at the end), so the step costs waves(S) * (tiles / S + 6).  The smallest S
+    within 3 % of the cheapest is taken, with at least 256 keys a split.
+    Measured (us, 32 query and 8 kv heads of 128): 8 sequences of 2,049 keys 16.8
+    with the 4 splits this picks (19.8 with 2, 21.7 with 8); 64 sequences 86.3 with
+    1 (99.4 with 2); one sequence 9.1 with 8 or 9 (17.7 with 2)."""
+    if DECODE_SPLITS_OVERRIDE:
+        return DECODE_SPLITS_OVERRIDE
+    places = per_sm * _sm_count(device)
+    pairs = max(1, n_seqs * nkv)
+    tiles = max(1, (max_kv_len + 63) // 64)
+    most = max(1, min(64, (max_kv_len + 255) // 256))
+    cost = {s: ((pairs * s + places - 1) // places) * (-(-tiles // s) + 6.0) for s in range(1, most + 1)}
+    best = min(cost.values())
+    return min(s for s, c in cost.items() if c <= 1.03 * best)
+
+
+@_profiled("attn_decode_tma", _cost_attention)
+def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: int, scale: float,
+                    max_kv_len: int, window: Optional[int] = None,
+                    n_splits: Optional[int] = None, stages: int = 0) -> torch.Tensor:
+    """Attention of one new token per sequence over its cached keys, the tiles
+    brought in by TMA and the splits combined by the block that finishes last (one
+    launch).  Heads of 64 or 128, pages of 64 tokens."""
+    _need(q, "q", torch.bfloat16, 3)
+    B, nq, D = q.shape
+    _need(k_pages, "k pages", torch.bfloat16, 4)
+    _need(v_pages, "v pages", torch.bfloat16, 4)
+    nkv = k_pages.shape[1]
+    if tuple(k_pages.shape[1:]) != (nkv, page, D) or v_pages.shape != k_pages.shape:
+        raise KernelError(f"pages are {tuple(k_pages.shape)}, expected [*, nkv, {page}, {D}]")
+    for t, nm in ((block_table, "block table"), (slots, "slots"), (kv_len, "kv_len")):
+        _need(t, nm, torch.int32)
+    if slots.shape[0] != B or kv_len.shape[0] != B:
+        raise KernelError("one slot and one length per query row are needed")
+    stages = int(stages or DECODE_TMA_STAGES)
+    per_sm = {0: 2, 2: 3, 3: 2, 4: 1}.get(stages, 2) if D == 128 else 3
+    ns = int(n_splits) if n_splits else decode_tma_splits(B, nkv, max_kv_len, q.device, per_sm)
+    out = torch.empty_like(q)
+    a = _DecodeTmaArgs()
+    if ns > 1:
+        ws = _WORKSPACES.setdefault(q.device.index or 0, _Workspace())
+        scratch, _c = ws.get(q.device, B * nq * ns * (D + 2), 1)
+        dev = q.device.index or 0
+        counters = _ATTN_COUNTERS.get(dev)
+        if counters is None or counters.numel() < B * nkv:
+            counters = _ATTN_COUNTERS[dev] = torch.zeros(max(B * nkv, 1 << 16), dtype=torch.int32,
+                                                         device=q.device)
+        a.part_o, a.part_ml = scratch.data_ptr(), scratch[B * nq * ns * D:].data_ptr()
+        a.counters = counters.data_ptr()
+    a.q, a.block_table, a.slots = q.data_ptr(), block_table.data_ptr(), slots.data_ptr()
+    a.kv_len, a.out, a.error = kv_len.data_ptr(), out.data_ptr(), _tc_error_flag(q.device).data_ptr()
+    a.n_seqs, a.nq, a.nkv, a.max_pages = B, nq, nkv, block_table.shape[1]
+    a.window, a.n_splits, a.scale_log2 = int(window or 0), ns, float(scale) * _LOG2E
+    with torch.cuda.device(q.device):
+        _check(_fn("attn_decode_tma", "gb_attn_decode_tma", "pplpiiip")(
+            k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], ctypes.addressof(a), D, page,
+            stages, _stream()), "attn_decode_tma")
+    return out
+
+
 # ---------------------------------------------------------------- attention dispatch
 def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float,
               window: Optional[int] = None) -> torch.Tensor:
@@ -921,6 +1021,13 @@ def attention(q, k_pages, v_pages, block_table, *, step, page: int, scale: float
     kernels where they accept the shape and the plain kernel elsewhere."""
     _T, nq, D = q.shape
     if q.dtype == torch.bfloat16 and fast_attention_takes(D, nq, k_pages.shape[1], page):
+        nkv = k_pages.shape[1]
+        if step.decode and attn_decode_tma_takes(D, nq, nkv, page) and (
+                DECODE_ATTENTION == "tma" or
+                (DECODE_ATTENTION == "auto" and step.n_seqs * nkv >= DECODE_TMA_PAIRS)):
+            return attn_decode_tma(q, k_pages, v_pages, block_table, slots=step.slots,
+                                   kv_len=step.kv_len, page=page, scale=scale,
+                                   max_kv_len=step.max_kv_len, window=window)
         if step.decode:
             return attn_decode_bf16(q, k_pages, v_pages, block_table, slots=step.slots,
                                     kv_len=step.kv_len, page=page, scale=scale,

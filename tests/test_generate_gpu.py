@@ -193,7 +193,8 @@ def test_command_line(model_dirs, plain_weights, tmp_path):
     prompt = random_tokens(9, 256, 780)
     out = str(tmp_path / "out.json")
     env = dict(os.environ, PYTHONPATH=ROOT)
-    for extra in (["--fp32"], ["--fp32", "--device-argmax", "--profile"]):
+    for extra in (["--fp32"], ["--fp32", "--device-argmax", "--profile"],
+                  ["--fp32", "--profile", "--profile-ops"]):
         r = subprocess.run([sys.executable, "-m", "grout_b200", "--model", model_dirs["A"],
                             "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "6",
                             "--ignore-eos", "--output-json", out] + extra,
@@ -204,6 +205,11 @@ def test_command_line(model_dirs, plain_weights, tmp_path):
         assert rec["token_ids"] == plain.greedy_generate(w, cfg, prompt, 6)
         assert rec["generated_tokens"] == 6 and rec["prompt_tokens"] == 9
     assert "profile:" in r.stdout
+    # the last run timed every operation: a row per kernel with its calls and rates
+    assert "op profile" in r.stdout
+    ops_rows = {l.split()[0]: l.split() for l in r.stdout.splitlines() if l.startswith("  ")}
+    for name in ("embed", "add_rmsnorm", "qk_prepare", "attn_generic", "gemm_f32"):
+        assert name in ops_rows and int(ops_rows[name][1]) > 0, (name, r.stdout[-2000:])
     # the bench binary's options: several measured generations, one JSON line each
     lines = str(tmp_path / "runs.jsonl")
     r = subprocess.run([sys.executable, "-m", "grout_b200", "--model", model_dirs["A"],

@@ -458,6 +458,78 @@ def test_attn_decode_bf16(nq, nkv, D, window, n_splits):
         assert torch.allclose(got[2, 0].double(), pc.v[2][5, 0].double(), atol=1e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("stages", [2, 3, 4])
+@pytest.mark.parametrize("n_splits", [1, 3, 11, None])     # 11: more partials than the merge requests at once
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("nq,nkv,D", [(8, 1, 128), (32, 8, 128), (6, 2, 64), (16, 1, 64)])
+def test_attn_decode_tma(nq, nkv, D, window, n_splits, stages):
+    """The decode attention whose tiles come by TMA and whose splits are combined by the
+    block that finishes last.  Rows of a page beyond a sequence's length hold NaN here:
+    the kernel masks them as keys and zeroes them as values.  Two launches in a row:
+    the second finds the arrival counters as the first left them (zero)."""
+    ops = _ops()
+    dt = torch.bfloat16
+    lens = [1, 130, 200, 64, 33, 65, 128, 129]
+    pc = Paged(lens, nkv, D, dt, 42)
+    B = len(lens) + 1                               # one padding row at the end
+    q = _rand((B, nq, D), dt, 43)
+    scale = 1.0 / math.sqrt(D)
+    if window is None:
+        q[2] = 0
+        q[2, :, 0] = 30.0
+        pc.k[2][:, :, 0] = 0
+        pc.k[2][5, :, 0] = 30.0
+        for j in range(lens[2]):
+            pc.store(2, j, pc.k[2][j], pc.v[2][j])
+    args = (q.to(DEV), pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV))
+    kw = dict(slots=torch.tensor(pc.slot_of + [-1], dtype=torch.int32, device=DEV),
+              kv_len=torch.tensor(lens + [7], dtype=torch.int32, device=DEV), page=64, scale=scale,
+              max_kv_len=256, window=window, n_splits=n_splits, stages=stages)
+    first = ops.attn_decode_tma(*args, **kw).cpu()
+    got = ops.attn_decode_tma(*args, **kw).cpu()
+    ops.check_kernel_errors()
+    assert torch.equal(first, got)
+    assert not torch.isnan(got.float()).any()
+    for s, n in enumerate(lens):
+        want = _attn_oracle(q[s], pc.k[s], pc.v[s], n - 1, scale, window)
+        assert torch.allclose(got[s].double(), want, **FAST_TOL), (s, n)
+    assert bool((got[B - 1] == 0).all())            # the padding row
+    if window is None:
+        assert torch.allclose(got[2, 0].double(), pc.v[2][5, 0].double(), atol=1e-2, rtol=1e-2)
+    # the kernel without TMA gives the same within rounding
+    other = ops.attn_decode_bf16(*args, **{k: v for k, v in kw.items() if k != "stages"}).cpu()
+    assert torch.allclose(got.float(), other.float(), **FAST_TOL)
+
+
+@pytest.mark.parametrize("n_splits", [1, 2, 5, None])
+def test_attn_decode_tma_long_sequences(n_splits):
+    """Long sequences, so that the ring of stages goes round many times; one query looks
+    at a single far key, whose value must come back."""
+    ops = _ops()
+    dt = torch.bfloat16
+    nq, nkv, D = 8, 2, 128
+    lens = [1500, 700, 33, 2049]
+    pc = Paged(lens, nkv, D, dt, 48)
+    q = _rand((len(lens), nq, D), dt, 49)
+    scale = 1.0 / math.sqrt(D)
+    q[0] = 0
+    q[0, :, 0] = 30.0
+    pc.k[0][:, :, 0] = 0
+    pc.k[0][777, :, 0] = 30.0
+    for j in range(lens[0]):
+        pc.store(0, j, pc.k[0][j], pc.v[0][j])
+    got = ops.attn_decode_tma(
+        q.to(DEV), pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV),
+        slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
+        kv_len=torch.tensor(lens, dtype=torch.int32, device=DEV), page=64, scale=scale,
+        max_kv_len=2112, n_splits=n_splits).cpu()
+    ops.check_kernel_errors()
+    for s, n in enumerate(lens):
+        want = _attn_oracle(q[s], pc.k[s], pc.v[s], n - 1, scale, None)
+        assert torch.allclose(got[s].double(), want, **FAST_TOL), (s, n)
+    assert torch.allclose(got[0, 0].double(), pc.v[0][777, 0].double(), atol=1e-2, rtol=1e-2)
+
+
 @pytest.mark.parametrize("n_splits", [1, 2, 5])
 def test_attn_decode_many_tiles_per_warp(n_splits):
     """Long sequences, so that each warp refills its key and value buffers many times (its
@@ -570,7 +642,8 @@ def _restore(pc, seq):
         pc.store(seq, j, pc.k[seq][j], pc.v[seq][j])
 
 
-@pytest.mark.parametrize("kernel", ["decode-1", "decode-3", "mma", "tc-128", "tc-256"])
+@pytest.mark.parametrize("kernel", ["decode-1", "decode-3", "tma-decode-1", "tma-decode-3", "mma",
+                                    "tc-128", "tc-256"])
 @pytest.mark.parametrize("nq,nkv,D", [(8, 2, 128), (6, 3, 64)])
 def test_the_window_edge_to_the_key(kernel, nq, nkv, D):
     """The tensor-core attention kernels at a window's edge, with keys planted so that
@@ -580,7 +653,7 @@ def test_the_window_edge_to_the_key(kernel, nq, nkv, D):
     ops = _ops()
     dt, W = torch.bfloat16, 70
     scale = 1.0 / math.sqrt(D)
-    if kernel.startswith("decode"):
+    if "decode" in kernel:
         # the one query of each sequence sits at its last position
         lens = [W + 64, W + 81, 3 * 64 + 5, W + 1]
         pc = Paged(lens, nkv, D, dt, 60)
@@ -591,11 +664,13 @@ def test_the_window_edge_to_the_key(kernel, nq, nkv, D):
             _plant_window_edge(q, s, pc, s, n - 1, W)
             _restore(pc, s)
             planted.append((s, s, n - 1))
-        got = ops.attn_decode_bf16(
+        run = ops.attn_decode_tma if kernel.startswith("tma") else ops.attn_decode_bf16
+        got = run(
             q.to(DEV), pc.k_pages.to(DEV), pc.v_pages.to(DEV), pc.table.to(DEV),
             slots=torch.tensor(pc.slot_of, dtype=torch.int32, device=DEV),
             kv_len=torch.tensor(lens, dtype=torch.int32, device=DEV), page=64, scale=scale,
             max_kv_len=512, window=W, n_splits=int(kernel[-1])).cpu()
+        ops.check_kernel_errors()
     else:
         # (tokens already held, tokens of this step); planted rows by position
         plan = [(0, 260), (50, 200)]
