@@ -176,16 +176,17 @@ def quartiles(xs):
 
 
 def run_ops(size: str, batch: int, layers: int, pk) -> int:
-    """One prompt step of 2,048 tokens and four decode steps of ``batch`` sequences,
-    launched kernel by kernel with an event pair around each: the table of
-    ``ops.OpProfile`` for each phase.  The times are those of kernels that run alone,
-    one after the other; inside a captured step they overlap at their edges."""
+    """One prompt step of 2,048 tokens launched kernel by kernel with an event pair
+    around each (the table of ``ops.OpProfile``: every kernel alone on the device),
+    and the decode step of ``batch`` sequences as it runs inside its captured graph
+    (``decode_timeline``)."""
     import torch
     from grout_b200.engine import Engine
     from grout_b200.kernels import ops
     cfg = dict(SIZES[size], num_hidden_layers=layers)
     eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=batch * (PROMPT + 128),
-                        max_batch=batch, max_seq_len=CONTEXT, use_graphs=False)
+                        max_batch=batch, max_seq_len=CONTEXT)
+    eng.use_graphs = False
     g = torch.Generator().manual_seed(1)
     V = cfg["vocab_size"]
 
@@ -205,18 +206,93 @@ def run_ops(size: str, batch: int, layers: int, pk) -> int:
     print(prof.report())
     for i in range(1, batch, 8):
         eng.step([(s, prompt()) for s in slots[i:i + 8]])
-    tok = torch.randint(0, V, (batch,), generator=g).tolist()
-    for _ in range(2):
-        eng.step([(s, [t]) for s, t in zip(slots, tok)], [[0]] * batch)
-    prof = ops.OpProfile(pk["hbm_gbs"], pk["bf16_tflops"])
-    ops.set_profile(prof)
-    for _ in range(4):
-        eng.step([(s, [t]) for s, t in zip(slots, tok)], [[0]] * batch)
-    ops.set_profile(None)
-    print(f"== 4 decode steps, batch {batch}, {PROMPT + 3}-{PROMPT + 6} keys a sequence")
-    print(prof.report())
     eng.check()
+    print(decode_timeline(eng, slots, V, g, pk))
     return 0
+
+
+def decode_timeline(eng, slots, V, g, pk, steps: int = 3) -> str:
+    """The kernels of a captured decode step as they ran inside it, from the activity
+    records of the CUDA profiling interface (torch.profiler): per kernel its calls a
+    step, its mean duration, and its mean *exposed* time, which is how much later it
+    ended than everything before it (kernels overlap at their edges: a kernel is
+    resident, fetching what no earlier kernel writes, while its predecessor drains).
+    The exposed times add up to the step.  Times taken under the profiler's tracing:
+    a breakdown, not a benchmark figure."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from grout_b200.kernels import ops
+    batch = len(slots)
+    eng.use_graphs = True
+    tok = torch.randint(0, V, (batch,), generator=g).tolist()
+
+    def step():
+        eng.step([(s, [t]) for s, t in zip(slots, tok)], [[0]] * batch)
+
+    # the capture of the step's graph (a warm-up pass and the captured pass) says, launch by
+    # launch, which product each kernel of the step is; kernel names alone do not
+    eng.graphs.decode_graphs.clear()
+    ops.LAUNCH_LOG = []
+    step()
+    graph = eng.graphs.decode(batch, max(eng.cache.length[s] for s in slots))
+    labels = ops.LAUNCH_LOG[-graph.kernels_per_replay:]         # the captured pass
+    ops.LAUNCH_LOG = None
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            step()
+        torch.cuda.synchronize()
+    ev = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+                 and "memcpy" not in e.name.lower() and "memset" not in e.name.lower()),
+                key=lambda e: e.time_range.start)
+    starts = [i for i, e in enumerate(ev) if "embed_kernel" in e.name]
+    rows, total = {}, 0.0
+    for a, b in zip(starts, starts[1:] + [len(ev)]):
+        frontier = ev[a].time_range.start
+        named = len(labels) == b - a
+        for k, e in enumerate(ev[a:b]):
+            end = e.time_range.end
+            name = labels[k] if named else e.name.split("(")[0].replace("void ", "")
+            r = rows.setdefault(name, [0, 0.0, 0.0])
+            r[0] += 1
+            r[1] += end - e.time_range.start
+            r[2] += max(0.0, end - frontier)
+            frontier = max(frontier, end)
+        total += frontier - ev[a].time_range.start
+    n = len(starts)
+    if n and len(labels) != len(ev) // n:
+        print(f"bench.py: {len(labels)} launches were logged for a step of {len(ev) // n} kernels; "
+              f"rows are named by kernel", file=sys.stderr)
+    kv = sum(eng.cache.length[s] for s in slots)
+    cfg = eng.config
+
+    def must_read(name):
+        """Bytes a call of this kernel has to read: a product its weights, the decode
+        attention the keys and values of the live sequences (one layer's)."""
+        part = name.split()
+        if part[0] == "gemm_tc_bf16" and len(part) > 1 and "x" in part[1]:
+            rows_w, cols_w = part[1].split("x")
+            return 2.0 * int(rows_w) * int(cols_w)
+        if part[0].startswith("attn_decode") and "second" not in name:
+            return 2.0 * kv * 2 * cfg.num_key_value_heads * cfg.head_dim
+        return None
+
+    lines = [f"== decode step, batch {batch}, {kv // batch} keys a sequence, as it ran inside the captured "
+             f"graph ({n} steps traced): {total / n:.1f} us a step; GB/s = what the kernel has to read / "
+             f"its exposed time, of the {pk['source']} {pk['hbm_gbs']:.0f} GB/s",
+             f"  {'kernel':<36}{'calls/step':>11}{'mean_us':>9}{'exposed_us':>11}{'per step':>10}{'share':>7}"
+             f"{'GB/s':>8}{'of hbm':>8}"]
+    for name, (calls, dur, exposed) in sorted(rows.items(), key=lambda kv: -kv[1][2]):
+        line = (f"  {name[:35]:<36}{calls / n:>11.1f}{dur / calls:>9.2f}{exposed / calls:>11.2f}"
+                f"{exposed / n:>10.1f}{exposed / total:>7.1%}")
+        nbytes = must_read(name)
+        if nbytes and exposed > 0:
+            gbs = nbytes / (exposed / calls * 1e-6) / 1e9
+            line += f"{gbs:>8.0f}{gbs / pk['hbm_gbs']:>8.2f}"
+        lines.append(line)
+    return "\n".join(lines)
 
 
 def main() -> int:

@@ -181,10 +181,15 @@ def _cost_qk_prepare(out, qkv, nq, nkv, D):
     return _nbytes(qkv, q) + kv_bytes, 0
 
 
-def _check(rc: int, what: str, kernels: int = 1) -> None:
+LAUNCH_LOG: Optional[list] = None     # when a list: one label per kernel launched, in order
+
+
+def _check(rc: int, what: str, kernels: int = 1, detail: str = "") -> None:
     global _LAUNCHES
     if rc == 0:
         _LAUNCHES += kernels
+        if LAUNCH_LOG is not None and kernels > 0:
+            LAUNCH_LOG.extend([what + detail] + [what + " (second kernel)"] * (kernels - 1))
         return
     if rc in _OWN_ERRORS:
         raise KernelError(f"{what}: {_OWN_ERRORS[rc]}")
@@ -662,7 +667,8 @@ def gemm_tc_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
         a.silu, a.dep_b = int(silu_mul), int(swap)      # the activations are another kernel's output
         a.stamps = _ptr(stamps)     # int64 [blocks, 8]: phase times of every block, for tuning
         _check(_fn("gemm_tc", "gb_gemm_tc_bf16", "pppp")(
-            A.data_ptr(), B.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc_bf16")
+            A.data_ptr(), B.data_ptr(), ctypes.addressof(a), _stream()), "gemm_tc_bf16",
+            detail=f" {N}x{K}" + (" silu" if silu_mul else "") + (f" split {split}" if split else ""))
     return y
 
 

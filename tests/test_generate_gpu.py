@@ -132,6 +132,19 @@ def test_limits(model_dirs):
     assert eng.generate([[1, 2]], 0)[0].token_ids == []
     with pytest.raises(ValueError, match="vocabulary"):
         eng.step([(eng.open_sequence(), [256])])
+    # a wanted place beyond the entry's tokens is refused on every path: prompt and decode
+    # steps, captured (bfloat16) or launched one by one (32-bit)
+    for dtype in ("float32", "bfloat16"):
+        e = _engine(model_dirs, "A", dtype)
+        s = e.open_sequence()
+        with pytest.raises(ValueError, match="outside the 3 tokens"):
+            e.step([(s, [1, 2, 3])], [[3]])
+        assert e.length(s) == 0                      # a refused step stores nothing
+        e.step([(s, [1, 2, 3])], [[2]])
+        with pytest.raises(ValueError, match="outside the 1 tokens"):
+            e.step([(s, [4])], [[1]])
+        assert e.step([(s, [4])], [[0]]).shape == (1, 256) and e.length(s) == 4
+        e.close_sequence(s)
 
 
 def test_looking_ahead_across_a_bucket_of_rows(model_dirs):
