@@ -156,14 +156,20 @@ __host__ __device__ inline int tc_ranges(int p, int P, int tiles, int kblocks, i
   return 0;
 }
 
-template <int BN>
+// LEAN: four stages for the 32- and 64-column tiles, so that two blocks share an SM.  A
+// split-K launch whose tiles x splits overshoot the SMs a little (80 tiles cut in two on
+// 148 SMs) then runs in one go instead of two waves: the qkv product of the widest
+// model at batch 64 took 36 us as 80 blocks (44 % of the copy peak) and takes 21 as
+// 160.  The large products keep six stages: with four, gate|up went from 102 to 117 us.
+template <int BN, int LEAN = 0>
 struct TcConfig {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // both multiples of 1024
   // (wide tiles: as deep a ring as shared memory allows; narrow ones: see TC_STAGES_16)
   static constexpr int STAGES =
-      BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? TC_STAGES_64 : (BN >= 32 ? TC_STAGES_32 : TC_STAGES_16)));
+      (LEAN && (BN == 32 || BN == 64)) ? 4
+      : BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? TC_STAGES_64 : (BN >= 32 ? TC_STAGES_32 : TC_STAGES_16)));
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256;
   // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
@@ -171,11 +177,11 @@ struct TcConfig {
                                     ((uint32_t)(TC_BM >> 4) << 24);
 };
 
-template <int BN>
+template <int BN, int LEAN = 0>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const TcArgs a, const int lead_share) {
-  using Cfg = TcConfig<BN>;
+  using Cfg = TcConfig<BN, LEAN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles_base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -632,7 +638,8 @@ static int tc_split(int rowsA, int rowsB, int K, int sms) {
   // Two blocks of the narrowest tiles fit on an SM, so a few more blocks than SMs cost
   // nothing, and one more cut fills the GPU where tiles * s falls well short of it
   // (40 tiles: 160 blocks instead of 120 on 148 SMs).
-  if (bn <= 16 && TC_SPLIT_OVER > 0 && tiles * (s + 1) <= sms + sms / TC_SPLIT_OVER) s += 1;
+  // (the 32- and 64-column tiles then take the launch with four stages: TcConfig's LEAN)
+  if (bn <= 64 && TC_SPLIT_OVER > 0 && tiles * (s + 1) <= sms + sms / TC_SPLIT_OVER) s += 1;
   if (s > kblocks / 4) s = kblocks / 4;
   if (s > 8) s = 8;
   return s < 2 ? 0 : (int)s;   // 0: not worth it (the product already has enough tiles)
@@ -692,17 +699,18 @@ static int tc_plan_for(int rowsA, int rowsB, int K, int sms, TcPlan* pl) {
   return 0;
 }
 
-template <int BN>
+template <int BN, int LEAN = 0>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, int blocks,
                   int lead_share, cudaStream_t s) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)TcConfig<BN>::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, LEAN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)TcConfig<BN, LEAN>::SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return gb_launch(gemm_tc_kernel<BN>, dim3(blocks), dim3(TC_THREADS), TcConfig<BN>::SMEM, s, ma, mb, a, lead_share);
+  return gb_launch(gemm_tc_kernel<BN, LEAN>, dim3(blocks), dim3(TC_THREADS), TcConfig<BN, LEAN>::SMEM, s, ma, mb,
+                   a, lead_share);
 }
 
 static int check_shape(int rowsA, int rowsB, int K) {
@@ -763,10 +771,12 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   TcPlan pl;
   e = tc_plan(args->rowsA, args->rowsB, args->K, &pl);
   if (e) return e;
+  bool lean = false;
   if (args->split_k > 0) {
     if (!args->transpose_out || !args->out_f32 || args->silu) return GB_ERR_UNSUPPORTED;
     const int tiles = ((args->rowsA + TC_BM - 1) / TC_BM) * ((args->rowsB + pl.bn - 1) / pl.bn);
     if (args->split_k > (args->K + TC_BK - 1) / TC_BK) return GB_ERR_BAD_ARG;
+    lean = (pl.bn == 32 || pl.bn == 64) && tiles * args->split_k > pl.blocks;   // more blocks than SMs
     pl.blocks = tiles * args->split_k;
     pl.lead_share = 0;
   }
@@ -777,8 +787,12 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   if (e) return e;
   switch (pl.bn) {
     case 16: return launch<16>(ma, mb, *args, pl.blocks, pl.lead_share, s);
-    case 32: return launch<32>(ma, mb, *args, pl.blocks, pl.lead_share, s);
-    case 64: return launch<64>(ma, mb, *args, pl.blocks, pl.lead_share, s);
+    case 32:
+      return lean ? launch<32, 1>(ma, mb, *args, pl.blocks, pl.lead_share, s)
+                  : launch<32>(ma, mb, *args, pl.blocks, pl.lead_share, s);
+    case 64:
+      return lean ? launch<64, 1>(ma, mb, *args, pl.blocks, pl.lead_share, s)
+                  : launch<64>(ma, mb, *args, pl.blocks, pl.lead_share, s);
     case 128: return launch<128>(ma, mb, *args, pl.blocks, pl.lead_share, s);
     case 256: return launch<256>(ma, mb, *args, pl.blocks, pl.lead_share, s);
   }

@@ -746,9 +746,20 @@ class _DecodeArgs(ctypes.Structure):
 
 _LOG2E = 1.4426950408889634
 PREFILL_ROWS = 64          # query rows per block of the prefill kernel
-FAST_ATTENTION_MODULES: Tuple[str, ...] = ("attn_prefill_tc", "attn_prefill_bf16",
-                                            "attn_decode_bf16", "attn_decode_tma")
 PREFILL_ATTENTION = "tc"      # "tc": tcgen05 where the shape allows; "mma": the mma.sync kernel
+
+
+def fast_attention_modules(D: int, nq: int, nkv: int, page: int = 64) -> Tuple[str, ...]:
+    """The tensor-core attention sources that heads of this shape can reach (a model
+    compiles what it needs and no more)."""
+    mods: Tuple[str, ...] = ()
+    if fast_attention_takes(D, nq, nkv, page):
+        mods += ("attn_prefill_bf16", "attn_decode_bf16")
+        if attn_prefill_tc_takes(D, nq, nkv, page):
+            mods += ("attn_prefill_tc",)
+        if attn_decode_tma_takes(D, nq, nkv, page):
+            mods += ("attn_decode_tma",)
+    return mods
 _SM_COUNT = {}
 
 

@@ -47,7 +47,14 @@ class Linear:
     def kernel_modules(self):
         if self.weight.dtype == torch.float32:
             return ("gemm_f32", "elementwise")
-        return ("gemm_tc", "gemm_tc2", "gemm_skinny_bf16")
+        if self.in_features % 8:
+            return ()                                  # only the library's product takes such a width
+        mods = ("gemm_tc",) if "tc" in (self.decode_kernel, self.prefill_kernel) else ()
+        if self.decode_kernel == "skinny":
+            mods += ("gemm_skinny_bf16",)
+        if self.prefill_kernel in ("auto", "pair"):
+            mods += ("gemm_tc2",)
+        return mods
 
     def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
                  partial_ok: bool = False) -> torch.Tensor:

@@ -102,7 +102,7 @@ class GQAAttention(Mixer):
     def kernel_modules(self):
         mods = ("qk_prepare", "attn_generic") + self.qkv.kernel_modules() + self.o.kernel_modules()
         if self.ctx.dtype == torch.bfloat16:
-            mods += ops.FAST_ATTENTION_MODULES
+            mods += ops.fast_attention_modules(self.D, self.nq, self.nkv)
         return mods
 
     def cache_spec(self):
