@@ -263,7 +263,10 @@ static int launch(const float* res_in, const void* delta, const float* parts, in
   // a row's sums may depend on the width alone, so that a token's result is the
   // same in a step of one row and in a step of thousands.
   constexpr bool by_rows_too = !std::is_same<T, float>::value;
-  if (by_rows_too && aligned && n_rows <= 64 && N >= 1024 && N % (4 * NC_CLUSTER) == 0 &&
+#ifndef NC_MAX_ROWS
+#define NC_MAX_ROWS 64
+#endif
+  if (by_rows_too && aligned && n_rows <= NC_MAX_ROWS && N >= 1024 && N % (4 * NC_CLUSTER) == 0 &&
       N / NC_CLUSTER <= 4096) {
     int threads = ((N / NC_CLUSTER / 4 + 31) / 32) * 32;
     return gb_launch_cluster(add_rmsnorm_cluster_kernel<T, WT>, dim3(n_rows * NC_CLUSTER),
