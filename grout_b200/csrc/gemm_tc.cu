@@ -638,22 +638,39 @@ static int tc_split(int rowsA, int rowsB, int K, int sms) {
   // Two blocks of the narrowest tiles fit on an SM, so a few more blocks than SMs cost
   // nothing, and one more cut fills the GPU where tiles * s falls well short of it
   // (40 tiles: 160 blocks instead of 120 on 148 SMs).
-  // (the 32- and 64-column tiles then take the launch with four stages: TcConfig's LEAN)
-  if (bn <= 64 && TC_SPLIT_OVER > 0 && tiles * (s + 1) <= sms + sms / TC_SPLIT_OVER) s += 1;
+  // The 32- and 64-column tiles get the extra cut only where they would otherwise not be
+  // cut at all (80 tiles on 148 SMs), and then take the launch with four stages
+  // (TcConfig's LEAN), which is what lets the 160 blocks run in one go.  Where they are
+  // cut anyway (20 tiles seven ways: 140 blocks) the GPU is full enough, and with six
+  // stages one more cut would mean a second wave.
+  if ((bn <= 16 || (bn <= 64 && s == 1)) && TC_SPLIT_OVER > 0 &&
+      tiles * (s + 1) <= sms + sms / TC_SPLIT_OVER)
+    s += 1;
   if (s > kblocks / 4) s = kblocks / 4;
   if (s > 8) s = 8;
   return s < 2 ? 0 : (int)s;   // 0: not worth it (the product already has enough tiles)
 }
 
 static int tc_plan_for(int rowsA, int rowsB, int K, int sms, TcPlan* pl);
-static int tc_plan(int rowsA, int rowsB, int K, TcPlan* pl) {
+// SMs of the current device (0 after an error, which the next call reports again).
+static int tc_sms(int* err) {
   static int sms = 0;
+  *err = 0;
   if (!sms) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return (int)e;
+    if (e != cudaSuccess) {
+      sms = 0;
+      *err = (int)e;
+    }
   }
+  return sms;
+}
+static int tc_plan(int rowsA, int rowsB, int K, TcPlan* pl) {
+  int e = 0;
+  const int sms = tc_sms(&e);
+  if (e) return e;
   return tc_plan_for(rowsA, rowsB, K, sms, pl);
 }
 // (the plan for a GPU of `sms` SMs: no device is asked, so a host-side test can call it)
@@ -776,7 +793,8 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
     if (!args->transpose_out || !args->out_f32 || args->silu) return GB_ERR_UNSUPPORTED;
     const int tiles = ((args->rowsA + TC_BM - 1) / TC_BM) * ((args->rowsB + pl.bn - 1) / pl.bn);
     if (args->split_k > (args->K + TC_BK - 1) / TC_BK) return GB_ERR_BAD_ARG;
-    lean = (pl.bn == 32 || pl.bn == 64) && tiles * args->split_k > pl.blocks;   // more blocks than SMs
+    int err = 0;
+    lean = (pl.bn == 32 || pl.bn == 64) && tiles * args->split_k > tc_sms(&err);   // more blocks than SMs
     pl.blocks = tiles * args->split_k;
     pl.lead_share = 0;
   }

@@ -35,6 +35,7 @@ PROMPT_TOKENS_MOST = 1024       # longer prompt steps are bound by the device, n
 PROMPT_SEQS_MOST = 64
 PROMPT_TOKENS_LEAST = 16
 PROMPT_GRAPHS_MOST = 48         # captured prompt shapes kept; further shapes run launch by launch
+PROMPT_LOGITS_MOST = 2 << 30    # bytes of logits the captured prompt shapes may hold between them
 LENGTH_LEAST = 512
 
 
@@ -223,6 +224,7 @@ class StepGraphs:
         self.model, self.cache, self.device, self.largest = model, cache, device, largest
         self.decode_graphs: Dict[Tuple[int, int], DecodeGraph] = {}
         self.prompt_graphs: Dict[Tuple[int, int, int], PromptGraph] = {}
+        self._prompt_logits_bytes = 0
         self._pool = None
         self._prompts_ok: Optional[bool] = None
 
@@ -255,8 +257,12 @@ class StepGraphs:
             return None
         g = self.prompt_graphs.get(key)
         if g is None:
-            if len(self.prompt_graphs) >= PROMPT_GRAPHS_MOST:
+            # every captured shape keeps its logits [wanted rows, vocabulary] allocated
+            held = 4 * key[2] * self.model.plan.vocab_size
+            if len(self.prompt_graphs) >= PROMPT_GRAPHS_MOST or \
+                    self._prompt_logits_bytes + held > PROMPT_LOGITS_MOST:
                 return None
+            self._prompt_logits_bytes += held
             g = self.prompt_graphs[key] = PromptGraph(self.model, self.cache, self.device,
                                                       self.pool(), *key)
         return g

@@ -160,7 +160,7 @@ def wide_engines(model_dirs):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])     # D: heads of 64, the TMA decode attention at 64 live
 @pytest.mark.parametrize("n_live", [20, 64])
 def test_many_live_sequences(wide_engines, oracle, name, dtype, n_live):
     """20 and 64 sequences of unequal lengths alive at once (the captured steps of 32
@@ -219,6 +219,28 @@ def test_captured_steps_against_steps_launched_one_by_one(model_dirs, oracle, dt
             assert torch.equal(outs[True][i], outs[False][i]), i
 
 
+def test_tma_decode_attention_inside_the_engine(model_dirs, oracle, monkeypatch):
+    """The decode attention whose tiles come by TMA is chosen from 128 (sequence, kv head)
+    pairs up; forced here for every decode step, so that single sequences, small batches,
+    sequences that end early and reused slots go through it inside the engine."""
+    from grout_b200.engine import Engine
+    from grout_b200.kernels import ops
+    monkeypatch.setattr(ops, "DECODE_ATTENTION", "tma")
+    eng = Engine.load(model_dirs["D"], dtype="bfloat16", max_tokens=4096, max_batch=8, max_seq_len=512)
+    V = TINY["D"]["vocab_size"]
+    toks = random_tokens(200, V, 1600)
+    assert_close(run_tail_decoded(eng, toks, tail=80), oracle("D", toks), "bfloat16", "tma decode, one sequence")
+    for b in range(2):
+        plan = [(1, 20), (7, 2), (64, 5), (130, 33), (63, 3)]
+        reqs = [random_tokens(p + d, V, 1610 + 10 * b + i) for i, (p, d) in enumerate(plan)]
+        got = run_batch(eng, reqs, [p for p, _ in plan])
+        for i, r in enumerate(reqs):
+            assert_close(got[i], oracle("D", r), "bfloat16", f"tma decode, batch {b} request {i}")
+    ops.check_kernel_errors()
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
 def test_fp32_cuts_agree_tightly(engines):
     """Whole, tail-decoded and batched runs of the 32-bit path differ by rounding
     only; a looser agreement would point at the cache or the batch."""
@@ -270,4 +292,30 @@ def test_prompt_products_on_pairs_of_sms_inside_the_engine(model_dirs, oracle):
     for g, r in zip(got, reqs):
         assert_close(g, oracle("D", r), "bfloat16", "pair products, batch")
     ops.check_kernel_errors()
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decoding_across_a_bucket_of_lengths(tmp_path_factory, dtype):
+    """Captured decode steps are kept per bound on the longest sequence (512, 1,024, ...).
+    Two sequences decode from 505 and 40 tokens past 512: the steps before and after the
+    boundary replay different graphs (with different splits of the attention over the
+    keys), and every position must still equal the plain implementation."""
+    import json
+    import os
+    from safetensors import safe_open
+    from grout_b200.engine import Engine
+    from grout_b200.weights import write_random_model
+    cfg = dict(TINY["D"], max_position_embeddings=1100)
+    d = write_random_model(cfg, 13, str(tmp_path_factory.mktemp("long")))
+    with safe_open(os.path.join(d, "model.safetensors"), "pt") as f:
+        w = {k: f.get_tensor(k) for k in f.keys()}
+    raw = json.load(open(os.path.join(d, "config.json")))
+    eng = Engine.load(d, dtype=dtype, max_tokens=2048, max_batch=4, max_seq_len=1100, use_graphs=True)
+    reqs = [random_tokens(505 + 20, cfg["vocab_size"], 1500), random_tokens(40 + 20, cfg["vocab_size"], 1501)]
+    got = run_batch(eng, reqs, [505, 40])
+    for g, r in zip(got, reqs):
+        assert_close(g, plain.logits(w, raw, r), dtype, "across the 512 boundary")
+    assert {512, 1024} <= {length for _b, length in eng.graphs.decode_graphs}
+    eng.check()
     eng.cache.check()
