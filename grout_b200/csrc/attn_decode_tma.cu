@@ -49,7 +49,14 @@ struct DecodeTmaArgs {
   int* error;              // device int, 0 while all is well
   int n_seqs, nq, nkv, max_pages, window, n_splits;
   float scale_log2;
+  unsigned long long* stamps;   // optional [blocks][12] %globaltimer stamps of a block's phases (tuning), or null
 };
+
+#define DA_STAMP(slot)                                                                          \
+  do {                                                                                          \
+    if (a.stamps)                                                                               \
+      a.stamps[(((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 12 + (slot)] = now_ns(); \
+  } while (0)
 
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(DA_CONSUMERS) : "memory");
@@ -99,6 +106,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   // newest key are requested before waiting for that kernel.
   const int fresh_tile = pos / DA_BN;
 
+  if (tid == 0) DA_STAMP(0);
   if (tid == DA_CONSUMERS) {      // the producer lane: have the descriptors fetched while the block sets up
     tma_prefetch_map(&map_k);
     tma_prefetch_map(&map_v);
@@ -144,13 +152,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
         for (int ds = 0; ds < DS; ++ds)
           tma_load_2d(st + HALF_BYTES + ds * (DA_BN * 128), &map_v, ds * 64, row0, &full_v[s]);
         *issued = it + 1;
+        if (it == 0) DA_STAMP(1);
       }
+      DA_STAMP(2);
     }
     return;
   }
 
   // ---- consumers ----------------------------------------------------------------
   pdl_wait();
+  if (tid == 0) DA_STAMP(3);
   WarpAttn<DT> w;
   w.init();
   if (my_tiles > 0) {
@@ -164,6 +175,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
     cp_async_commit();
     cp_async_wait<0>();
     consumer_sync();
+    if (tid == 0) DA_STAMP(4);
     w.load_q(q_s);
     int lo[2] = {key_lo, key_lo}, hi[2] = {pos, pos};
     bool ok = true;
@@ -177,6 +189,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
         ok = false;
         break;
       }
+      if (tid == 0 && it == 0) DA_STAMP(5);
       const int valid = kv_len - (t_begin + it) * DA_BN;       // rows of the page that hold keys
       bool wrote = false;
       auto between = [&] {
@@ -212,6 +225,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
     }
   }
   pdl_launch_dependents();   // the key stream of this block is over
+  if (tid == 0) DA_STAMP(6);
   consumer_sync();
   if (*abort_flag && warp == 0 && lane == 0) {
     // let the copies that were issued and not consumed land before the block leaves
@@ -230,18 +244,21 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
     float* red = reinterpret_cast<float*>(stages);
     float* red_m = red;                               // [warps][16]
     float* red_l = red + DA_WARPS * 16;               // [warps][16]
-    float* red_o = red + 2 * DA_WARPS * 16;           // [warps][16][D]
+    float* red_o = red + 2 * DA_WARPS * 16;           // [warps][16][D + 8]
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int row = g + r * 8;
-      if (t == 0) {
-        red_m[warp * 16 + row] = w.m[r];
-        red_l[warp * 16 + row] = w.l[r];
-      }
+      if (row < G) {          // the rows beyond the group's heads are padding: nobody reads them
+        if (t == 0) {
+          red_m[warp * 16 + row] = w.m[r];
+          red_l[warp * 16 + row] = w.l[r];
+        }
+        // rows are D + 8 floats apart so that the eight rows a warp stores at once fall
+        // into different banks
 #pragma unroll
-      for (int i = 0; i < 2 * DT; ++i) {
-        red_o[((size_t)warp * 16 + row) * D + i * 8 + t * 2] = w.o[i][2 * r];
-        red_o[((size_t)warp * 16 + row) * D + i * 8 + t * 2 + 1] = w.o[i][2 * r + 1];
+        for (int i = 0; i < 2 * DT; ++i)
+          *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + row) * (D + 8) + i * 8 + t * 2) =
+              make_float2(w.o[i][2 * r], w.o[i][2 * r + 1]);
       }
     }
     consumer_sync();
@@ -256,7 +273,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
         const float mw = red_m[wi * 16 + row];
         const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
         L += red_l[wi * 16 + row] * f;
-        O += red_o[((size_t)wi * 16 + row) * D + d] * f;
+        O += red_o[((size_t)wi * 16 + row) * (D + 8) + d] * f;
       }
       if (single) {
         a.out[((size_t)seq * a.nq + h0 + row) * D + d] = __float2bfloat16(O / L);
@@ -292,8 +309,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
   if (single) return;
 
   // ---- count in; the block that arrives last combines the splits ------------------
+  if (tid == 0) DA_STAMP(7);
   __threadfence();
   consumer_sync();
+  if (tid == 0) DA_STAMP(8);
   if (tid == 0) {
     int* counter = a.counters + (size_t)seq * a.nkv + kvh;
     const int before = atomicAdd(counter, 1);
@@ -303,6 +322,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
     }
   }
   consumer_sync();
+  if (tid == 0) DA_STAMP(9);
   if (!last_s) return;
   __threadfence();
   // Eight neighbouring columns of one head per thread and pass.  The loads of a pass do
@@ -360,6 +380,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k,
     packed.w = pack_bf16(O[6] * inv, O[7] * inv);
     *reinterpret_cast<uint4*>(a.out + ((size_t)seq * a.nq + h0 + row) * D + d0) = packed;
   }
+  if (tid == 0) DA_STAMP(10);
 }
 
 template <int DS, int STAGES>

@@ -91,6 +91,33 @@ __device__ __forceinline__ float fast_exp2(float x) {   // 2^x, one MUFU operati
   return y;
 }
 
+// The softmax threads are bound by how many instructions they issue as much as by the
+// exponentials, so the arithmetic around the exponentials is done two values at a time
+// (the packed 32-bit operations of this architecture) and the maximum three at a time.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {   // a * b + c, both halves
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
 template <int DS, int G>   // head_dim = 64 * DS; G query blocks of 128 rows per thread block
 struct AtConfig {
   static constexpr int D = 64 * DS;
@@ -438,7 +465,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < AT_BN; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+      for (int c = 0; c < AT_BN; c += 8) {
+        mx4[0] = max3(mx4[0], s[c], s[c + 1]);
+        mx4[1] = max3(mx4[1], s[c + 2], s[c + 3]);
+        mx4[2] = max3(mx4[2], s[c + 4], s[c + 5]);
+        mx4[3] = max3(mx4[3], s[c + 6], s[c + 7]);
+      }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
 
       // raise the base only when the maximum outgrew it by 2^8 (or on the first keys)
@@ -473,16 +505,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 3)
 
       const float mbase = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint64_t sum4[4] = {0ull, 0ull, 0ull, 0ull};       // four pairs of partial sums (0.0f, 0.0f)
       uint32_t pk[AT_BN / 2];
+      const uint64_t scale2 = pack_f32x2(a.scale_log2, a.scale_log2), base2 = pack_f32x2(-mbase, -mbase);
 #pragma unroll
       for (int c = 0; c < AT_BN; c += 2) {
-        const float e0 = fast_exp2(fmaf(s[c], a.scale_log2, -mbase));
-        const float e1 = fast_exp2(fmaf(s[c + 1], a.scale_log2, -mbase));
-        sum4[(c >> 1) & 3] += e0 + e1;
+        float x0, x1;
+        unpack_f32x2(fma_f32x2(pack_f32x2(s[c], s[c + 1]), scale2, base2), x0, x1);
+        const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
+        sum4[(c >> 1) & 3] = add_f32x2(sum4[(c >> 1) & 3], pack_f32x2(e0, e1));
         pk[c / 2] = pack2(e0, e1);
       }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      {
+        float lo, hi;
+        unpack_f32x2(add_f32x2(add_f32x2(sum4[0], sum4[1]), add_f32x2(sum4[2], sum4[3])), lo, hi);
+        l += lo + hi;
+      }
       AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 4)
 
       // P into shared memory, K-major [128 rows][64 keys] under the 128-byte swizzle.

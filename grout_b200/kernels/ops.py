@@ -942,22 +942,27 @@ class _DecodeTmaArgs(ctypes.Structure):
     _fields_ = [("q", _P), ("block_table", _P), ("slots", _P), ("kv_len", _P), ("out", _P),
                 ("part_o", _P), ("part_ml", _P), ("counters", _P), ("error", _P), ("n_seqs", _I),
                 ("nq", _I), ("nkv", _I), ("max_pages", _I), ("window", _I), ("n_splits", _I),
-                ("scale_log2", _F)]
+                ("scale_log2", _F), ("stamps", _P)]
 
 
+DECODE_TMA_STAMPS: Optional[torch.Tensor] = None      # int64 [blocks, 12] for tuning, or None
 _TC_ERROR_NAMES[131] = "a role of the decode attention kernel waited 2 s on a barrier"
 # Which decode attention runs: "auto" takes the TMA kernel where the shape allows and the
-# step has at least DECODE_TMA_PAIRS (sequence, kv head) pairs, and the cp.async kernel for
-# fewer; "tma" and "mma" force one.  Measured inside the decode step at 32 query and 8 kv
-# heads of 128 with 2,100 keys a sequence (ms a step, cp.async / TMA): 64 sequences 6.41 /
-# 5.99, 8 sequences 2.74 / 2.78, one sequence 2.38 / 2.48.  Timed by itself, one call after
-# the other, the TMA kernel is the faster or the equal at every size (16.8 against 17.9 us at
-# 8 sequences, 86 against 97 at 64); inside a step, where a short kernel comes before it, its
-# longer start (descriptor fetch, barrier set-up, the hand-over from the loading lane) shows
-# when there are few blocks to hide it behind.
+# step has at least DECODE_TMA_PAIRS (sequence, kv head) pairs, with two stages (three blocks
+# an SM) below DECODE_TMA_DEEP_PAIRS pairs and three stages (two blocks an SM) from there
+# on, and the cp.async kernel for fewer pairs; "tma" and "mma" force one.  Measured inside
+# the decode step at 32 query and 8 kv heads of 128 with 2,100 keys a sequence (ms a step,
+# cp.async / TMA with two stages / with three): 1 sequence 2.38 / 2.50 / 2.48, 4 sequences
+# 2.57 / 2.57 / 2.55, 8 sequences 2.74 / 2.72 / 2.78, 16 sequences 3.19 / 3.10 / 3.18, 32
+# sequences 4.35 / 4.27 / 4.04, 64 sequences 6.41 / 6.22 / 5.99.  Timed by itself, one call
+# after the other, the TMA kernel is the faster or the equal at every size (16.8 against
+# 17.9 us at 8 sequences, 86 against 97 at 64); inside a step of very few sequences, where
+# a short kernel comes before it, its longer start (descriptor fetch, barrier set-up, the
+# hand-over from the loading lane) shows.
 DECODE_ATTENTION = "auto"
-DECODE_TMA_PAIRS = 128
-DECODE_TMA_STAGES = 0         # tiles of a block in shared memory (0: the kernel's default)
+DECODE_TMA_PAIRS = 64
+DECODE_TMA_DEEP_PAIRS = 256
+DECODE_TMA_STAGES = 0         # tiles of a block in shared memory (0: by the number of pairs)
 _ATTN_COUNTERS = {}
 
 
@@ -1004,8 +1009,8 @@ def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: in
         _need(t, nm, torch.int32)
     if slots.shape[0] != B or kv_len.shape[0] != B:
         raise KernelError("one slot and one length per query row are needed")
-    stages = int(stages or DECODE_TMA_STAGES)
-    per_sm = {0: 2, 2: 3, 3: 2, 4: 1}.get(stages, 2) if D == 128 else 3
+    stages = int(stages or DECODE_TMA_STAGES) or (2 if B * nkv < DECODE_TMA_DEEP_PAIRS else 3)
+    per_sm = {2: 3, 3: 2, 4: 1}.get(stages, 2) if D == 128 else 3
     ns = int(n_splits) if n_splits else decode_tma_splits(B, nkv, max_kv_len, q.device, per_sm)
     out = torch.empty_like(q)
     a = _DecodeTmaArgs()
@@ -1023,6 +1028,7 @@ def attn_decode_tma(q, k_pages, v_pages, block_table, *, slots, kv_len, page: in
     a.kv_len, a.out, a.error = kv_len.data_ptr(), out.data_ptr(), _tc_error_flag(q.device).data_ptr()
     a.n_seqs, a.nq, a.nkv, a.max_pages = B, nq, nkv, block_table.shape[1]
     a.window, a.n_splits, a.scale_log2 = int(window or 0), ns, float(scale) * _LOG2E
+    a.stamps = _ptr(DECODE_TMA_STAMPS)
     with torch.cuda.device(q.device):
         _check(_fn("attn_decode_tma", "gb_attn_decode_tma", "pplpiiip")(
             k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], ctypes.addressof(a), D, page,
