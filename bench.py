@@ -350,7 +350,7 @@ def main() -> int:
     cfg = dict(SIZES[args.size], num_hidden_layers=layers)
     torch.manual_seed(0)
     biggest = max(args.batch, 64 if "points" in phases else 1)
-    room = PROMPT + W + K + 64
+    room = PROMPT + max(W + K, 129) + 64
     eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=biggest * ((room + 63) // 64 * 64),
                         max_batch=biggest, max_seq_len=CONTEXT)
     g = torch.Generator().manual_seed(1)
@@ -460,14 +460,16 @@ def main() -> int:
     # ---- end to end through the Python entry point -----------------------------------
     e2e = None
     if "e2e" in phases:
-        n_new = K + 1
+        # at least 128 decode steps: the first thirty after the prompts run at the clocks the
+        # power cap left behind, and a request of a few tokens would measure little else
+        n_new = max(K, 128) + 1
         prompts = [prompt() for _ in range(args.batch)]
         eng.generate(prompts, 4, ignore_eos=True)              # warm-up
         outs = eng.generate(prompts, n_new, ignore_eos=True)
         e2e_tps = sum(o.generated_tokens - 1 for o in outs) / outs[0].decode_elapsed
         graph = eng.graphs.decode(args.batch, PROMPT + n_new)
         h2d = int(graph.dev.numel() * 4) if graph is not None else 0
-        e2e = {"value": round(e2e_tps, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+        e2e = {"value": round(e2e_tps, 1), "unit": "tok/s", "steps": n_new - 1, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": 4 * args.batch}
 
     eng.check()      # a kernel that gave up on a bounded wait would have voided the numbers
