@@ -688,13 +688,24 @@ def gemm_tc2_takes(n_out: int, out_dtype) -> bool:
     return (n_out * (4 if out_dtype == torch.float32 else 2)) % 16 == 0
 
 
-def gemm_tc2_rounds(M: int, N: int, device) -> float:
-    """How many rounds of 256 x 256 tiles, one per pair of SMs, the product takes."""
+def gemm_tc2_pays(M: int, N: int, device, fused_silu: bool) -> bool:
+    """Whether the pair product is at least as fast as the library's for this shape.
+    It is for the gate|up product with its fused SiLU when the rounds of tiles it runs
+    are mostly full: the useful share M N / (whole rounds x pairs x 256 x 256) is at
+    least 3/4.  Measured (us, pair / library product plus SiLU kernel; N 19,456, K 2,560):
+    384 rows (share 0.51) 52 / 39, 512 (0.69) 53 / 51, 768 (0.77) 68 / 69, 1,024 (0.82)
+    84 / 85, 2,048 (0.91) 149 / 162; N 51,200, K 5,120: 128 rows (0.45) 109 / 106, 256
+    (0.90) 115 / 133, 384 (0.68) 193 / 165, 2,048 (0.98) 722 / 821.  A product without an
+    epilogue to fuse never pays: 6,144 x 2,560 at 2,048 rows 47.0 / 46.2, 10,240 x 5,120
+    172.7 / 157.2, and the library is ahead at every smaller row count."""
+    if not fused_silu:
+        return False
+    pairs = max(1, _sm_count(device) // 2)
     tiles = ((M + 255) // 256) * ((N + 255) // 256)
-    return tiles / max(1, _sm_count(device) // 2)
+    whole_rounds = (tiles + pairs - 1) // pairs
+    return 4 * M * N >= 3 * whole_rounds * pairs * 256 * 256
 
 
-@_profiled("gemm_tc2_bf16", _cost_gemm)
 def gemm_tc2_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                   silu_mul: bool = False, tile_cols: int = 0) -> torch.Tensor:
     """x [M, K] . w [N, K]^T for many rows on pairs of SMs (tcgen05.mma.cta_group::2,

@@ -11,15 +11,15 @@ It picks the product by the weight's precision and by the number of rows:
   kernel (``gemm_skinny_bf16``).
 * bf16 weight, more rows (a prompt): ``products.prefill = "auto"`` takes the product
   on pairs of SMs (``gemm_tc2_bf16``, tcgen05.mma.cta_group::2) where it is at
-  least as fast as the library's product, which is when its 256 x 256 tiles fill
-  at least two rounds on the GPU's pairs of SMs (the qkv product and the fused
-  gate|up product with its SiLU epilogue), and the library's product elsewhere,
-  where the reference uses a library too (cuBLAS GemmEx, src/cublas.rs:287-307).
-  ``"pair"`` takes the pair product for everything it can store, ``"tc"`` the
-  single-SM tcgen05 kernel in its other orientation, ``"library"`` the library
-  throughout.  Measured at 2,048 rows (us, library / pair): qkv 50 / 51, o 35 / 48,
-  gate|up 140 + 24 for SiLU / 145 fused, down 73 / 102 (o and down are 80 tiles on
-  74 pairs of SMs: a second round for six tiles).
+  least as fast as the library's product, which is the fused gate|up product with
+  its SiLU epilogue when its rounds of 256 x 256 tiles on the GPU's pairs of SMs
+  are mostly full (``ops.gemm_tc2_pays`` has the measurements), and the library's
+  product elsewhere, where the reference uses a library too (cuBLAS GemmEx,
+  src/cublas.rs:287-307).  ``"pair"`` takes the pair product for everything it can
+  store, ``"tc"`` the single-SM tcgen05 kernel in its other orientation,
+  ``"library"`` the library throughout.  Measured at 2,048 rows (us, library /
+  pair): qkv 46 / 47, o 35 / 48, gate|up 140 + 24 for SiLU / 149 fused, down 73 / 102
+  (o and down are 80 tiles on 74 pairs of SMs: a second round for six tiles).
 """
 from __future__ import annotations
 
@@ -80,7 +80,7 @@ class Linear:
             if ops.gemm_tc2_takes(self.out_features, out_dtype) and (
                     self.prefill_kernel == "pair" or
                     (self.prefill_kernel == "auto" and
-                     ops.gemm_tc2_rounds(M, self.out_features, x.device) >= 2.0)):
+                     ops.gemm_tc2_pays(M, self.out_features, x.device, fused_silu=False))):
                 return ops.gemm_tc2_bf16(x, w, out_dtype)
         return ops.library_mm(x, w, out_dtype)
 
@@ -98,6 +98,6 @@ class Linear:
                 and self.in_features % 8 == 0 and self.out_features % 32 == 0
                 and (self.prefill_kernel == "pair" or
                      (self.prefill_kernel == "auto" and
-                      ops.gemm_tc2_rounds(x.shape[0], self.out_features, x.device) >= 2.0))):
+                      ops.gemm_tc2_pays(x.shape[0], self.out_features, x.device, fused_silu=True)))):
             return ops.gemm_tc2_bf16(x, w, x.dtype, silu_mul=True)
         return ops.silu_mul(self(x), interleave)
