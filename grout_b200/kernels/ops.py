@@ -706,6 +706,7 @@ def gemm_tc2_pays(M: int, N: int, device, fused_silu: bool) -> bool:
     return 4 * M * N >= 3 * whole_rounds * pairs * 256 * 256
 
 
+@_profiled("gemm_tc2_bf16", _cost_gemm)
 def gemm_tc2_bf16(x: torch.Tensor, w: torch.Tensor, out_dtype=torch.bfloat16,
                   silu_mul: bool = False, tile_cols: int = 0) -> torch.Tensor:
     """x [M, K] . w [N, K]^T for many rows on pairs of SMs (tcgen05.mma.cta_group::2,
