@@ -179,7 +179,7 @@ __global__ void add_rmsnorm_cluster_kernel(const float* res_in, const T* delta, 
                            const WT* __restrict__ w, float eps, float* res_out,
                            T* __restrict__ y, int N) {
   __shared__ float scratch[32];
-  __shared__ float ss_mine;
+  __shared__ float ss_all[NC_CLUSTER];
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank();
   pdl_launch_dependents_if_small();
@@ -223,12 +223,14 @@ __global__ void add_rmsnorm_cluster_kernel(const float* res_in, const T* delta, 
     if (res_out) Vec4<float>::store(res_out + (size_t)r * N + i, v);
   }
   ss = block_sum(ss, scratch);
-  if (threadIdx.x == 0) ss_mine = ss;
+  // every block puts its sum into every block's table (thread k writes to block k), so
+  // that one cluster barrier is enough: after it each block reads its own shared memory
+  // only, and nobody is read from after it has left
+  if (threadIdx.x < NC_CLUSTER) cluster.map_shared_rank(ss_all, threadIdx.x)[rank] = ss;
   cluster.sync();
   float total = 0.f;
 #pragma unroll
-  for (int k = 0; k < NC_CLUSTER; ++k) total += *cluster.map_shared_rank(&ss_mine, k);
-  cluster.sync();   // nobody leaves while its sum may still be read
+  for (int k = 0; k < NC_CLUSTER; ++k) total += ss_all[k];
   const float inv = 1.0f / sqrtf(total / (float)N + eps);
   if (active) {
     float o[4];
