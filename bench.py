@@ -296,6 +296,7 @@ def decode_timeline(eng, slots, V, g, pk, steps: int = 3) -> str:
 
 
 def main() -> int:
+    global PROMPT, CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
@@ -306,6 +307,9 @@ def main() -> int:
                     help="layer sizes of the run (default: the 4B sizes the contract names)")
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT,
+                    help="tokens every sequence holds before decoding, and of the timed prompt step "
+                         "(default: the 2,048 the contract names; other lengths for the profiles)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--phases", default="prefill,decode,points,e2e",
                     help="which measurements to run (a profiler wants one at a time)")
@@ -327,6 +331,12 @@ def main() -> int:
         return 2
     if args.requests:
         return run_requests(args.requests, max(1, args.reps))
+    if args.prompt_len != PROMPT:
+        if not 1 <= args.prompt_len <= 36864:
+            print("bench.py: --prompt-len must be 1..36864", file=sys.stderr)
+            return 2
+        PROMPT = args.prompt_len
+        CONTEXT = max(CONTEXT, (PROMPT + 2048 + 63) // 64 * 64)
     full_layers = SIZES[args.size]["num_hidden_layers"]
     layers = args.layers or full_layers
     pk = peaks()
@@ -349,8 +359,13 @@ def main() -> int:
 
     cfg = dict(SIZES[args.size], num_hidden_layers=layers)
     torch.manual_seed(0)
-    biggest = max(args.batch, 64 if "points" in phases else 1)
     room = PROMPT + max(W + K, 129) + 64
+    point_batches = [1, 64] if "points" in phases else []
+    # (a cache for 64 sequences of a long prompt does not fit beside the weights: such a
+    # run keeps the batch-1 point only)
+    if 64 * room * kv_bytes_per_token(cfg, layers) > 100e9:
+        point_batches = [b for b in point_batches if b * room * kv_bytes_per_token(cfg, layers) <= 100e9]
+    biggest = max([args.batch] + point_batches)
     eng = Engine.random(cfg, 0, dtype="bfloat16", max_tokens=biggest * ((room + 63) // 64 * 64),
                         max_batch=biggest, max_seq_len=CONTEXT)
     g = torch.Generator().manual_seed(1)
@@ -391,8 +406,9 @@ def main() -> int:
     # ---- decode --------------------------------------------------------------------
     def decode_run(batch, steps, warm, sample_clocks=False):
         slots = [eng.open_sequence() for _ in range(batch)]
-        for i in range(0, batch, 8):                       # prompts go in, eight at a time
-            eng.step([(s, prompt()) for s in slots[i:i + 8]])
+        group = max(1, min(8, 16384 // PROMPT))            # prompts go in, 16,384 tokens at a time
+        for i in range(0, batch, group):
+            eng.step([(s, prompt()) for s in slots[i:i + group]])
         # the decode step as generation runs it: tokens chosen on the device (greedy)
         # feed the next step, which is queued without waiting for the host
         first = torch.randint(0, V, (batch,), generator=g).tolist()
@@ -450,8 +466,8 @@ def main() -> int:
                "value_at_median": round(args.batch / med * 1e3, 1)}
 
     points = {}
-    if "points" in phases:
-        for bsz in (1, 64):
+    if point_batches:
+        for bsz in point_batches:
             m, _l, c, _, _p = decode_run(bsz, 32, 4)
             points[f"decode_b{bsz}"] = round(bsz * 32 / m * 1e3, 1)
             points[f"decode_b{bsz}_hbm_frac"] = round(

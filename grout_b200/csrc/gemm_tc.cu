@@ -25,8 +25,12 @@
 // at the tile's counter, which adds the 32-bit partials (kept in scratch, two
 // slots per block) in block order.  No block waits for another block.
 //
-// Leftover deal (lead_share = S > 0, chosen by the host for wide tiles when there are a
-// few more tiles than blocks): block p owns tile p whole, and the tiles beyond the
+// One tile per block: when a product has more tiles than the GPU has SMs but all of them
+// fit on it at once (two or three blocks an SM), the launch has as many blocks as tiles
+// and the rule above gives every block exactly one whole tile; nothing is shared.
+//
+// Leftover deal (lead_share = S > 0, chosen by the host when there are a few more tiles
+// than blocks and the tiles do not all fit at once): block p owns tile p whole, and the tiles beyond the
 // P-th are cut S ways over K among blocks 0 .. (tiles - P) S - 1, each of which takes
 // its share BEFORE its own tile.  The shares end early and together, so the block that
 // adds them does it while its own tile streams, and no block streams two whole tiles.
@@ -156,11 +160,12 @@ __host__ __device__ inline int tc_ranges(int p, int P, int tiles, int kblocks, i
   return 0;
 }
 
-// LEAN: four stages for the 32- and 64-column tiles, so that two blocks share an SM.  A
-// split-K launch whose tiles x splits overshoot the SMs a little (80 tiles cut in two on
-// 148 SMs) then runs in one go instead of two waves: the qkv product of the widest
-// model at batch 64 took 36 us as 80 blocks (44 % of the copy peak) and takes 21 as
-// 160.  The large products keep six stages: with four, gate|up went from 102 to 117 us.
+// LEAN: four stages for the tiles of up to 64 columns, so that one more block fits on an SM
+// (two of the 32- and 64-column tiles, three of the 16-column ones).  A launch with a few
+// more blocks than the GPU otherwise holds at once then runs in one go instead of two
+// waves: the qkv product of the widest model at batch 64, 80 tiles cut in two, took 36 us
+// as 80 blocks (44 % of the copy peak) and takes 21 as 160.  Where the blocks fit anyway the
+// products keep six stages: with four, a gate|up product went from 102 to 117 us.
 template <int BN, int LEAN = 0>
 struct TcConfig {
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
@@ -168,7 +173,7 @@ struct TcConfig {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // both multiples of 1024
   // (wide tiles: as deep a ring as shared memory allows; narrow ones: see TC_STAGES_16)
   static constexpr int STAGES =
-      (LEAN && (BN == 32 || BN == 64)) ? 4
+      (LEAN && BN <= 64) ? 4
       : BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? TC_STAGES_64 : (BN >= 32 ? TC_STAGES_32 : TC_STAGES_16)));
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256;
@@ -623,7 +628,22 @@ static int pick_bn(int rowsB) {
 struct TcPlan {
   int bn, blocks, scratch_floats, counters;
   int lead_share;   // > 0: the leftover deal with that many shares per leftover tile
+  int lean;         // 1: the launch with four stages (TcConfig's LEAN)
 };
+
+// Blocks of a tile width that one SM holds at once (by shared memory: 227 KB an SM, a
+// kilobyte reserved per block), with the usual ring of stages or the lean one.
+static int tc_blocks_per_sm(int bn, bool lean) {
+  size_t smem = 0;
+  switch (bn) {
+    case 16: smem = lean ? TcConfig<16, 1>::SMEM : TcConfig<16>::SMEM; break;
+    case 32: smem = lean ? TcConfig<32, 1>::SMEM : TcConfig<32>::SMEM; break;
+    case 64: smem = lean ? TcConfig<64, 1>::SMEM : TcConfig<64>::SMEM; break;
+    case 128: smem = TcConfig<128>::SMEM; break;
+    default: smem = TcConfig<256>::SMEM; break;
+  }
+  return (int)((227 * 1024) / (smem + 1024));
+}
 
 // How many ways K is cut when the consumer adds the partials (split_k mode): as
 // many blocks as fill the GPU once, at least four k-blocks each, at most 8 ways.
@@ -695,6 +715,7 @@ static int tc_plan_for(int rowsA, int rowsB, int K, int sms, TcPlan* pl) {
   // Failing that, for wide tiles, a number of blocks that divides the tiles, so that no
   // tile is shared.
   pl->lead_share = 0;
+  pl->lean = 0;
   if (tiles > sms) {
     const int kblocks = (K + TC_BK - 1) / TC_BK;
     long long s = sms / (tiles - sms);   // as many shares as there are blocks to take them,
@@ -702,7 +723,19 @@ static int tc_plan_for(int rowsA, int rowsB, int K, int sms, TcPlan* pl) {
     const int most = bn <= 16 ? TC_LEAD_SHARE_16 : (bn <= 32 ? TC_LEAD_SHARE_32 : TC_LEAD_SHARE_64);
     if (s > most) s = most;   // and not more than the adding block reads in passing
     const long long per = (tiles + sms - 1) / sms;
-    if (tiles < 2 * (long long)sms && s >= 2) {
+    // More tiles than SMs, but all of them fit on the GPU at once (two or three blocks an
+    // SM): one whole tile per block and no tile shared.  The blocks stream side by side and
+    // the memory system divides its bandwidth among them, not among the SMs, so the SMs
+    // that hold one block more do not finish later.  Measured against the leftover deal
+    // below (us exposed inside the decode step; rows x K of the weight, batch): 19,456 x
+    // 2,560, 152 tiles: 19.3 against 20.4 at batch 8, 23.1 against 27.3 at batch 64; 24,576
+    // x 4,096, 192 tiles: 34.3 against 36.9 at batch 8.
+    if (tiles <= (long long)sms * tc_blocks_per_sm(bn, false)) {
+      blocks = tiles;
+    } else if (bn <= 64 && tiles <= (long long)sms * tc_blocks_per_sm(bn, true)) {
+      blocks = tiles;
+      pl->lean = 1;
+    } else if (tiles < 2 * (long long)sms && s >= 2) {
       blocks = sms;
       pl->lead_share = (int)s;
     } else if (bn >= 64 && tiles % per == 0 && tiles / per >= sms / 2) {
@@ -757,7 +790,7 @@ GB_EXPORT int gb_gemm_tc_plan(int rowsA, int rowsB, int K, int* plan) {
 }
 
 // For host-side tests, no device needed.  plan[0..4] as above for a GPU of `sms` SMs, plan[5] =
-// shares of the leftover deal (0: none).
+// shares of the leftover deal (0: none), plan[6] = 1 for the launch with four stages.
 GB_EXPORT int gb_gemm_tc_plan_for(int rowsA, int rowsB, int K, int sms, int* plan) {
   int e = check_shape(rowsA, rowsB, K);
   if (e) return e;
@@ -768,6 +801,7 @@ GB_EXPORT int gb_gemm_tc_plan_for(int rowsA, int rowsB, int K, int sms, int* pla
   plan[0] = pl.bn, plan[1] = pl.blocks, plan[2] = pl.scratch_floats, plan[3] = pl.counters;
   plan[4] = tc_split(rowsA, rowsB, K, sms);
   plan[5] = pl.lead_share;
+  plan[6] = pl.lean;
   return 0;
 }
 // ranges[0..3] = rb0, re0, rb1, re1 of block p of P (see tc_ranges).
@@ -788,7 +822,7 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   TcPlan pl;
   e = tc_plan(args->rowsA, args->rowsB, args->K, &pl);
   if (e) return e;
-  bool lean = false;
+  bool lean = pl.lean != 0;
   if (args->split_k > 0) {
     if (!args->transpose_out || !args->out_f32 || args->silu) return GB_ERR_UNSUPPORTED;
     const int tiles = ((args->rowsA + TC_BM - 1) / TC_BM) * ((args->rowsB + pl.bn - 1) / pl.bn);
@@ -804,7 +838,9 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
   e = make_map(&mb, B, args->rowsB, args->K, pl.bn);
   if (e) return e;
   switch (pl.bn) {
-    case 16: return launch<16>(ma, mb, *args, pl.blocks, pl.lead_share, s);
+    case 16:
+      return lean ? launch<16, 1>(ma, mb, *args, pl.blocks, pl.lead_share, s)
+                  : launch<16>(ma, mb, *args, pl.blocks, pl.lead_share, s);
     case 32:
       return lean ? launch<32, 1>(ma, mb, *args, pl.blocks, pl.lead_share, s)
                   : launch<32>(ma, mb, *args, pl.blocks, pl.lead_share, s);

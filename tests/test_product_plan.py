@@ -1,6 +1,7 @@
 """The work plan of the tcgen05 matrix product, checked on the host: for every way of
 dealing the (tile, k-block) units of a product to the blocks of a launch (equal shares of
-the line, the leftover deal, split-K for the consumer), the blocks' ranges, computed by
+the line, one whole tile per block when all blocks fit on the GPU at once, the leftover
+deal, split-K for the consumer), the blocks' ranges, computed by
 the same function the kernel runs, must cover every unit exactly once; shares of one tile
 must be consecutive blocks, as the block that adds them assumes.  No GPU is needed: the
 library is compiled by nvcc and only its host functions are called."""
@@ -23,9 +24,10 @@ def _lib():
 
 
 def _plan(lib, rows_a, rows_b, k, sms):
-    out = (ctypes.c_int * 6)()
+    out = (ctypes.c_int * 7)()
     assert lib.gb_gemm_tc_plan_for(rows_a, rows_b, k, sms, out) == 0
-    return dict(bn=out[0], blocks=out[1], scratch=out[2], counters=out[3], split=out[4], lead=out[5])
+    return dict(bn=out[0], blocks=out[1], scratch=out[2], counters=out[3], split=out[4], lead=out[5],
+                lean=out[6])
 
 
 def _ranges(lib, p, blocks, tiles, kblocks, split, lead):
@@ -65,14 +67,24 @@ def test_every_unit_is_worked_exactly_once(sms):
         assert bn in (16, 32, 64, 128, 256) and (bn >= rows_b or bn == 256)
         tiles = -(-rows_a // BM) * -(-rows_b // bn)
         kblocks = -(-k // BK)
-        assert pl["counters"] == tiles and 1 <= pl["blocks"] <= max(sms, 1)
+        assert pl["counters"] == tiles and 1 <= pl["blocks"]
         assert pl["scratch"] == 2 * pl["blocks"] * bn * BM
+        if pl["blocks"] > sms:
+            # more blocks than SMs only when every tile has a block of its own and all of
+            # them fit on the GPU at once: two of the 16-column tiles an SM with the usual
+            # ring of stages; three of them, or two of the 32- and 64-column ones, with four
+            per_sm = {(16, 0): 2, (16, 1): 3, (32, 1): 2, (64, 1): 2}.get((bn, pl["lean"]))
+            assert per_sm is not None and pl["blocks"] == tiles <= per_sm * sms and not pl["lead"], pl
+        else:
+            assert not pl["lean"]
         # the launch without split-K: equal shares, or the leftover deal
         seen, by_tile, longest = _cover(lib, pl["blocks"], tiles, kblocks, 0, pl["lead"])
         assert set(seen) == {1}, (rows_a, rows_b, k, sms, pl)
         for t, ps in by_tile.items():
             uniq = sorted(set(ps))
             assert uniq == list(range(uniq[0], uniq[-1] + 1)), (t, uniq)      # consecutive blocks
+        if pl["blocks"] == tiles:
+            assert all(len(set(ps)) == 1 for ps in by_tile.values())              # no tile is shared
         if pl["lead"]:
             n_left = tiles - pl["blocks"]
             assert pl["blocks"] == sms and 0 < n_left and n_left * pl["lead"] <= sms and pl["lead"] >= 2
