@@ -94,6 +94,31 @@ __device__ __forceinline__ float fast_exp2(float x) {   // 2^x, one MUFU operati
 // The softmax threads are bound by how many instructions they issue as much as by the
 // exponentials, so the arithmetic around the exponentials is done two values at a time
 // (the packed 32-bit operations of this architecture) and the maximum three at a time.
+// An arrival by the lanes for which pred holds, as a predicated instruction: no branch for
+// the warp to diverge at and come together after.
+__device__ __forceinline__ void mbar_arrive_if(void* bar, bool pred) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %1, 0;\n\t@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}" ::"r"(
+                   smem_u32(bar)),
+               "r"((uint32_t)pred)
+               : "memory");
+}
+// A wait for a thread that is far ahead of what it waits for (the producer, by the depth of
+// its ring): it sleeps between polls instead of taking issue slots from the warps that work.
+__device__ __forceinline__ bool mbar_wait_idle(void* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;
+  const unsigned long long t0 = now_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i) {
+      __nanosleep(200);
+      if (mbar_try(bar, parity)) return true;
+    }
+    if (*abort_flag) return mbar_try(bar, parity);
+    if (now_ns() - t0 > TC_WAIT_LIMIT_NS) return false;
+  }
+}
+__device__ __forceinline__ void sts128(uint32_t saddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(saddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -125,7 +150,9 @@ struct AtConfig {
   // which share an SM (two stages each): finer pieces of work for the SMs to share out
   // when a step has few query rows, and the two blocks overlap like the two query blocks.
   static constexpr int STAGES = G == 2 ? 4 : 2;
-  static constexpr int THREADS = G == 2 ? 352 : 192;
+  static constexpr int NSW = 4;                             // softmax warps per query block
+  static constexpr int MMA_B_WARP = 2 + G * NSW;            // (G = 2 only) the issuing warp of block B
+  static constexpr int THREADS = 32 * (2 + G * NSW + (G == 2 ? 1 : 0));
   static constexpr int SUB_BYTES = AT_BN * 128;             // one [64 keys][64] sub-tile
   static constexpr int KV_BYTES = 2 * DS * SUB_BYTES;       // K and V of one stage
   static constexpr int P_BYTES = AT_BM * 128;               // [128][64 keys]; two per query block
@@ -172,7 +199,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   __shared__ int abort_s;
   volatile int* abort_flag = &abort_s;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // (taken from lane 0, so that the compiler knows it is the same in the whole warp)
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0), lane = threadIdx.x & 31;
   const int h = blockIdx.x;
 #ifdef AT_BLOCK_STAMPS
   unsigned long long* bst = (unsigned long long*)(a.error + 64) + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8;
@@ -231,14 +259,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       mbar_init(&kv_empty[AT_STAGES + s], 1);
     }
     for (int g = 0; g < 2; ++g) {
-      mbar_init(&q_full[g], 4);    // one arrival per softmax warp of the group
+      mbar_init(&q_full[g], Cfg::NSW);    // one arrival per softmax warp of the group
       mbar_init(&s_full[g], 1);
-      mbar_init(&s_empty[g], 4);
+      mbar_init(&s_empty[g], Cfg::NSW);
       mbar_init(&o_done[g], 1);
       mbar_init(&o_final[g], 1);
     }
     for (int i = 0; i < 4; ++i) {   // (with one query block the second half is unused)
-      mbar_init(&p_full[i], 4);
+      mbar_init(&p_full[i], Cfg::NSW);
     }
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -264,8 +292,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const int s = j % AT_STAGES;
         // the tile that held this stage has been read by the query blocks that needed it
         const uint32_t par = (((uint32_t)(j / AT_STAGES)) & 1) ^ 1;
-        bool freed = j - AT_STAGES >= n_a || mbar_wait(&kv_empty[s], par, abort_flag);
-        freed = freed && (j - AT_STAGES >= n_b || mbar_wait(&kv_empty[AT_STAGES + s], par, abort_flag));
+        bool freed = j - AT_STAGES >= n_a || mbar_wait_idle(&kv_empty[s], par, abort_flag);
+        freed = freed && (j - AT_STAGES >= n_b || mbar_wait_idle(&kv_empty[AT_STAGES + s], par, abort_flag));
         if (!freed) {
           if (!*abort_flag) atomicCAS(a.error, 0, GB_ERR_AT_TIMEOUT);
           *abort_flag = 1;
@@ -282,7 +310,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       }
       pdl_launch_dependents();
     }
-  } else if (warp == 1 || warp == 10) {
+  } else if (warp == 1 || (G == 2 && warp == Cfg::MMA_B_WARP)) {
     // ------------------------------------------------------------------ MMA issue
     // One warp per query block.  The whole warp walks an event loop: three lanes
     // test the three barriers that the next products wait for, all at once, a
@@ -389,7 +417,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
   } else {
     // ------------------------------------------------------------------ softmax and store
-    const int g = (warp - 2) >> 2;                 // query block of this warp (warps 2-9)
+    // One thread per query row.  What a warp does per tile is a chain (barrier, TMEM load,
+    // maximum, exponentials, store, fence, barrier) whose length is set by how many
+    // instructions it issues and by their latencies, not by the special-function unit (taking
+    // the exponentials out changes nothing; neither does halving either product or leaving
+    // out the loads): so every instruction that is not arithmetic on the 64 values counts.
+    // (Two threads a row, for four warps per scheduler instead of two, was no faster: the
+    // per-tile instructions that do not shrink with the values are then paid twice.)
+    constexpr int NSW = Cfg::NSW;
+    const int idx = warp - 2;
+    const int g = idx / NSW;                       // query block of this warp
     const int q = warp & 3;                        // the TMEM lanes this warp may touch
     const int r = q * 32 + lane;                   // query row inside the block
     const int pos = pos0 + g * AT_BM + r;
@@ -400,6 +437,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const uint32_t o_addr = lane_addr + Cfg::TMEM_O + g * D;
     const uint32_t s_addr = lane_addr + Cfg::TMEM_S + g * AT_BN;
     const int n_mine = g ? n_b : n_a;
+    // a tile wholly at or below the block's first position P (and inside every row's
+    // window) needs no mask: the first that does is the one whose last key lies beyond P
+    const int j_mask = (a.window > 0 || rows_mine < AT_BM) ? 0 : max(0, (pos0 + g * AT_BM + 1) / AT_BN - tile_lo);
+    const uint32_t p_row = smem_u32(p_s + (g * 2) * Cfg::P_BYTES + r * 128), p_swz = (uint32_t)(r & 7) << 4;
     float m_used = -INFINITY, l = 0.f;             // base of the exponent (scaled), row sum
     bool ok = true;
 #ifdef AT_STAMPS
@@ -409,7 +450,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     auto wait_warp = [&](uint64_t* bar, uint32_t parity) -> bool {
       return mbar_wait_warp(bar, parity, nullptr);
     };
-
     if (n_mine > 0) {
       // this thread's query row into its lane of tensor memory: 32-bit word c of
       // the row (elements 2c and 2c+1) is column c
@@ -430,48 +470,53 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&q_full[g]);
+      mbar_arrive_if(&q_full[g], lane == 0);
     }
 
-    for (int j = 0; j < n_mine && ok; ++j) {
+    for (int j = 0; j < n_mine; ++j) {
       const int b = j & 1;
+      float s[AT_BN];
+      float mx;
+      const int key0 = (tile_lo + j) * AT_BN;
+      const bool need_mask = j >= j_mask;
       AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 0)
       if (!wait_warp(&s_full[g], ((uint32_t)j) & 1)) { ok = false; break; }
-      tc_fence_after();
-      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 1)
-      float s[AT_BN];
       {
-        uint32_t v[AT_BN];
-        tc_ld64(s_addr, v);
-        tc_wait_ld();
+        tc_fence_after();
+        AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 1)
+        {
+          uint32_t v[AT_BN];
+          tc_ld64(s_addr, v);
+          tc_wait_ld();
 #pragma unroll
-        for (int jj = 0; jj < AT_BN; ++jj) s[jj] = __uint_as_float(v[jj]);
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[g]);   // S is in registers: the next S may be written
-      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 2)
-
-      const int key0 = (tile_lo + j) * AT_BN;
-      // a tile wholly at or below the block's first position (and inside every
-      // row's window) needs no mask
-      const bool need_mask = key0 + AT_BN - 1 > pos0 + g * AT_BM || a.window > 0 || rows_mine < AT_BM;
-      if (need_mask) {
-#pragma unroll
-        for (int c = 0; c < AT_BN; ++c) {
-          const int key = key0 + c;
-          if (key < lo || key > hi) s[c] = -INFINITY;
+          for (int jj = 0; jj < AT_BN; ++jj) s[jj] = __uint_as_float(v[jj]);
         }
-      }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        tc_fence_before();
+        __syncwarp();
+        mbar_arrive_if(&s_empty[g], lane == 0);   // S is in registers: the next S may be written
+        AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 2)
+        if (need_mask) {
+          const int last = hi - key0, first = lo - key0;   // this row's keys of the tile
+          if (a.window > 0) {
 #pragma unroll
-      for (int c = 0; c < AT_BN; c += 8) {
-        mx4[0] = max3(mx4[0], s[c], s[c + 1]);
-        mx4[1] = max3(mx4[1], s[c + 2], s[c + 3]);
-        mx4[2] = max3(mx4[2], s[c + 4], s[c + 5]);
-        mx4[3] = max3(mx4[3], s[c + 6], s[c + 7]);
+            for (int c = 0; c < AT_BN; ++c)
+              if (c < first || c > last) s[c] = -INFINITY;
+          } else {
+#pragma unroll
+            for (int c = 0; c < AT_BN; ++c)
+              if (c > last) s[c] = -INFINITY;
+          }
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < AT_BN; c += 8) {
+          mx4[0] = max3(mx4[0], s[c], s[c + 1]);
+          mx4[1] = max3(mx4[1], s[c + 2], s[c + 3]);
+          mx4[2] = max3(mx4[2], s[c + 4], s[c + 5]);
+          mx4[3] = max3(mx4[3], s[c + 6], s[c + 7]);
+        }
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * a.scale_log2;
 
       // raise the base only when the maximum outgrew it by 2^8 (or on the first keys)
       float factor = 1.0f;
@@ -486,7 +531,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       if (rescale) {
         // S_j is complete, so the product of tile j-2, issued before it, is too:
         // o_done is at most one phase behind
-
         if (!wait_warp(&o_done[g], ((uint32_t)(j - 1)) & 1)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
@@ -526,19 +570,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       // P into shared memory, K-major [128 rows][64 keys] under the 128-byte swizzle.
       // The buffer is free: S_j was issued after the product of tile j-2, which read
       // this buffer last, and the tensor core completes in order.
-      AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 5)
       {
-        uint8_t* prow = p_s + (g * 2 + b) * Cfg::P_BYTES + r * 128;
+        const uint32_t prow = p_row + b * Cfg::P_BYTES;
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          const uint4 w = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
-          *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = w;
-        }
+        for (int ch = 0; ch < AT_BN / 8; ++ch)
+          sts128(prow + ((uint32_t)(ch << 4) ^ p_swz), pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // visible to the tensor core
       AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 6)
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[g * 2 + b]);
+      mbar_arrive_if(&p_full[g * 2 + b], lane == 0);
       AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 7)
     }
 
@@ -556,13 +597,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const float inv = 1.0f / l;
       bf16* orow = a.out + ((size_t)(tok0 + g * AT_BM + r) * a.nq + h) * D;
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 64) {
-        uint32_t v[64];
-        tc_ld64(o_addr + c0, v);          // warp-wide: every lane loads, valid rows store
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t v[32];
+        tc_ld32(o_addr + c0, v);          // warp-wide: every lane loads, valid rows store
         tc_wait_ld();
         if (r < rows_mine) {
 #pragma unroll
-          for (int c = 0; c < 64; c += 8) {
+          for (int c = 0; c < 32; c += 8) {
             uint4 w;
             w.x = pack2(__uint_as_float(v[c]) * inv, __uint_as_float(v[c + 1]) * inv);
             w.y = pack2(__uint_as_float(v[c + 2]) * inv, __uint_as_float(v[c + 3]) * inv);
