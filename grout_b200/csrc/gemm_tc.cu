@@ -828,7 +828,20 @@ GB_EXPORT int gb_gemm_tc_bf16(const void* A, const void* B, const TcArgs* args, 
     const int tiles = ((args->rowsA + TC_BM - 1) / TC_BM) * ((args->rowsB + pl.bn - 1) / pl.bn);
     if (args->split_k > (args->K + TC_BK - 1) / TC_BK) return GB_ERR_BAD_ARG;
     int err = 0;
-    lean = (pl.bn == 32 || pl.bn == 64) && tiles * args->split_k > tc_sms(&err);   // more blocks than SMs
+    // Four stages, two blocks an SM, for the 32- and 64-column tiles: where there are more
+    // blocks than SMs, so that they run in one go; and where a block's share of K is short
+    // (TC_LEAN_SHARE k-blocks of 64 at most), because the product is then a short kernel between
+    // short kernels, and with room for a second block on every SM the next product's blocks
+    // are resident and fetching weights while this one's finish (with six stages of 24 KB a
+    // block has the SM to itself).  Measured, decode steps at batch 64 (ms, six stages / four
+    // for every cut product / four by this rule): Qwen3-4B sizes 5.91 / 5.82, 3.78 / 3.70 with
+    // 512 keys a sequence, 3.93 / 3.85 at batch 32; 8B sizes 7.04 / 7.05; 32B sizes 19.39 /
+    // 19.86, whose shares are 43 to 133 k-blocks long and want the deeper ring.
+#ifndef TC_LEAN_SHARE
+#define TC_LEAN_SHARE 32
+#endif
+    const int share = ((args->K + TC_BK - 1) / TC_BK + args->split_k - 1) / args->split_k;
+    lean = (pl.bn == 32 || pl.bn == 64) && (tiles * args->split_k > tc_sms(&err) || share <= TC_LEAN_SHARE);
     pl.blocks = tiles * args->split_k;
     pl.lead_share = 0;
   }
