@@ -507,9 +507,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
               if (c > last) s[c] = -INFINITY;
           }
         }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        // (the accumulators start from the first values, not from constants that would
+        // have to be loaded into registers every tile)
+        float mx4[4] = {fmaxf(s[0], s[1]), fmaxf(s[2], s[3]), fmaxf(s[4], s[5]), fmaxf(s[6], s[7])};
 #pragma unroll
-        for (int c = 0; c < AT_BN; c += 8) {
+        for (int c = 8; c < AT_BN; c += 8) {
           mx4[0] = max3(mx4[0], s[c], s[c + 1]);
           mx4[1] = max3(mx4[1], s[c + 2], s[c + 3]);
           mx4[2] = max3(mx4[2], s[c + 4], s[c + 5]);
@@ -549,7 +551,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       AT_STAMP(stamp_buf, (g * 4 + (j - 8)) * 8 + 3)
 
       const float mbase = (m_used == -INFINITY) ? 0.f : m_used;
-      uint64_t sum4[4] = {0ull, 0ull, 0ull, 0ull};       // four pairs of partial sums (0.0f, 0.0f)
+      uint64_t sum4[4];                                  // four pairs of partial sums
       uint32_t pk[AT_BN / 2];
       const uint64_t scale2 = pack_f32x2(a.scale_log2, a.scale_log2), base2 = pack_f32x2(-mbase, -mbase);
 #pragma unroll
@@ -557,7 +559,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         float x0, x1;
         unpack_f32x2(fma_f32x2(pack_f32x2(s[c], s[c + 1]), scale2, base2), x0, x1);
         const float e0 = fast_exp2(x0), e1 = fast_exp2(x1);
-        sum4[(c >> 1) & 3] = add_f32x2(sum4[(c >> 1) & 3], pack_f32x2(e0, e1));
+        if (c < 8) sum4[c >> 1] = pack_f32x2(e0, e1);
+        else sum4[(c >> 1) & 3] = add_f32x2(sum4[(c >> 1) & 3], pack_f32x2(e0, e1));
         pk[c / 2] = pack2(e0, e1);
       }
       {
