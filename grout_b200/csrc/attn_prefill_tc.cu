@@ -331,12 +331,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const uint32_t tq = tmem_base + Cfg::TMEM_Q + g * (D / 2);
     const uint32_t ts = tmem_base + Cfg::TMEM_S + g * AT_BN;
     const uint32_t to = tmem_base + Cfg::TMEM_O + g * D;
+    // The descriptors of stage 0 and of this block's first P buffer, once: a descriptor holds
+    // its address in 16-byte units in its low bits, so those of another stage or buffer are
+    // a sum (everything lies below 256 KB, the sum stays inside the field).
+    static_assert((AT_STAGES & (AT_STAGES - 1)) == 0, "stages are picked with a mask");
+    const uint64_t dk0 = make_smem_desc(smem_u32(kv_s));
+    const uint64_t dv0 = make_smem_desc_mn(smem_u32(kv_s + DS * Cfg::SUB_BYTES), Cfg::SUB_BYTES);
+    const uint64_t dp0 = make_smem_desc(smem_u32(p_s + (g * 2) * Cfg::P_BYTES));
     while (o_next < n_mine) {
       // lane 0: K/V of the tile S_g wants; lane 1: Q_g in place (first tile) or S_g
       // free; lane 2: P_g written.  Branch-free: one test instruction.
       bool mine = true;
       {
-        uint64_t* bar = &kv_full[s_next % AT_STAGES];
+        uint64_t* bar = &kv_full[s_next & (AT_STAGES - 1)];
         uint32_t par = ((uint32_t)(s_next / AT_STAGES)) & 1;
         bool need = s_next < n_mine;
         if (lane == 1) {
@@ -356,14 +363,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       // O_g += P_g V of the next tile
       if (o_next < s_next && (ready >> 2 & 1)) {
         const int t = o_next;
-        const uint32_t pa = smem_u32(p_s + (g * 2 + (t & 1)) * Cfg::P_BYTES);
-        const uint32_t va = smem_u32(kv_s + (size_t)(t % AT_STAGES) * Cfg::KV_BYTES + DS * Cfg::SUB_BYTES);
+        const int st = t & (AT_STAGES - 1);
         // four products of 16 keys: 32 bytes of a P row, 2 key groups of V each
         static_assert(AT_BN == 64, "one burst covers a key tile");
-        tc_mma_burst4_w<true>(to, make_smem_desc(pa), make_smem_desc_mn(va, Cfg::SUB_BYTES), 2,
-                              (2 * 1024) >> 4, Cfg::IDESC_R, t > 0 ? 1u : 0u, &o_done[g]);
+        tc_mma_burst4_w<true>(to, dp0 + (uint64_t)((t & 1) * (Cfg::P_BYTES >> 4)),
+                              dv0 + (uint64_t)(st * (Cfg::KV_BYTES >> 4)), 2, (2 * 1024) >> 4, Cfg::IDESC_R,
+                              t > 0 ? 1u : 0u, &o_done[g]);
         // K_t and V_t go back to the producer when the products so far are done
-        tc_commit_w(&kv_empty[g * AT_STAGES + t % AT_STAGES]);
+        tc_commit_w(&kv_empty[g * AT_STAGES + st]);
         if (t == n_mine - 1) tc_commit_w(&o_final[g]);
         o_next = t + 1;
         issued = true;
@@ -376,14 +383,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       // tile t-2 has been read, and that O_g holds all but the last product.
       if (s_next < n_mine && o_next + 1 >= s_next && (ready & 1) && (ready >> 1 & 1)) {
         const int t = s_next;
-        const uint32_t ka = smem_u32(kv_s + (size_t)(t % AT_STAGES) * Cfg::KV_BYTES);
+        const uint64_t dkt = dk0 + (uint64_t)((t & (AT_STAGES - 1)) * (Cfg::KV_BYTES >> 4));
         // per product 16 elements of head_dim: 8 columns of Q, 32 bytes of a K row
         if (DS == 1) {
-          tc_mma_ta_burst4_w<true>(ts, tq, make_smem_desc(ka), 2, Cfg::IDESC_S, 0u, &s_full[g]);
+          tc_mma_ta_burst4_w<true>(ts, tq, dkt, 2, Cfg::IDESC_S, 0u, &s_full[g]);
         } else {
 #pragma unroll
           for (int ds = 0; ds < DS; ++ds) {
-            const uint64_t dk = make_smem_desc(ka + ds * Cfg::SUB_BYTES);
+            const uint64_t dk = dkt + (uint64_t)(ds * (Cfg::SUB_BYTES >> 4));
             if (ds + 1 < DS) tc_mma_ta_burst4_w<false>(ts, tq + ds * 32, dk, 2, Cfg::IDESC_S, ds > 0 ? 1u : 0u, nullptr);
             else tc_mma_ta_burst4_w<true>(ts, tq + ds * 32, dk, 2, Cfg::IDESC_S, 1u, &s_full[g]);
           }
