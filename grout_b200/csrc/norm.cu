@@ -172,7 +172,9 @@ __global__ void add_rmsnorm_vec_kernel(const float* res_in, const T* delta, cons
 // columns, the sums of squares meet through distributed shared memory (added in
 // rank order, so the result is a fixed sum), and every block scales its columns.
 // The cluster barrier is the hardware's; no block spins on memory.
+#ifndef NC_CLUSTER
 #define NC_CLUSTER 4
+#endif
 template <typename T, typename WT>
 __global__ void add_rmsnorm_cluster_kernel(const float* res_in, const T* delta, const float* parts, int n_parts,
                            long long part_stride, const int* __restrict__ rows,
