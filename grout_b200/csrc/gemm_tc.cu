@@ -741,6 +741,26 @@ static int tc_plan_for(int rowsA, int rowsB, int K, int sms, TcPlan* pl) {
     } else if (bn >= 64 && tiles % per == 0 && tiles / per >= sms / 2) {
       blocks = tiles / per;
     }
+#ifndef TC_NO_WHOLE_TILES
+    // Too many tiles for one each even with four stages (400 tiles of 32 or 64 columns: the
+    // gate|up product of the widest model): a few whole tiles per block, if the tiles divide
+    // so and the blocks then fit at once, rather than equal shares of the line, which share
+    // nearly every tile between two blocks.
+    if (bn >= 32 && bn <= 64 && tiles > (long long)sms * tc_blocks_per_sm(bn, true)) {
+      for (long long k = 2; k <= per + 1; ++k) {
+        if (tiles % k) continue;
+        const long long b = tiles / k;
+        if (b <= sms) {
+          blocks = b, pl->lean = 0, pl->lead_share = 0;
+          break;
+        }
+        if (b <= (long long)sms * tc_blocks_per_sm(bn, true)) {
+          blocks = b, pl->lean = 1, pl->lead_share = 0;
+          break;
+        }
+      }
+    }
+#endif
   }
   pl->bn = bn;
   pl->blocks = (int)blocks;

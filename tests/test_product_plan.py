@@ -70,11 +70,13 @@ def test_every_unit_is_worked_exactly_once(sms):
         assert pl["counters"] == tiles and 1 <= pl["blocks"]
         assert pl["scratch"] == 2 * pl["blocks"] * bn * BM
         if pl["blocks"] > sms:
-            # more blocks than SMs only when every tile has a block of its own and all of
-            # them fit on the GPU at once: two of the 16-column tiles an SM with the usual
-            # ring of stages; three of them, or two of the 32- and 64-column ones, with four
+            # more blocks than SMs only when every block has whole tiles of its own (one, or
+            # for the 32- and 64-column tiles a few) and all blocks fit on the GPU at once: two
+            # of the 16-column tiles an SM with the usual ring of stages; three of them, or two
+            # of the 32- and 64-column ones, with four
             per_sm = {(16, 0): 2, (16, 1): 3, (32, 1): 2, (64, 1): 2}.get((bn, pl["lean"]))
-            assert per_sm is not None and pl["blocks"] == tiles <= per_sm * sms and not pl["lead"], pl
+            assert per_sm is not None and pl["blocks"] <= per_sm * sms and not pl["lead"], pl
+            assert tiles % pl["blocks"] == 0 and (pl["blocks"] == tiles or bn in (32, 64)), pl
         else:
             assert not pl["lean"]
         # the launch without split-K: equal shares, or the leftover deal
@@ -83,7 +85,7 @@ def test_every_unit_is_worked_exactly_once(sms):
         for t, ps in by_tile.items():
             uniq = sorted(set(ps))
             assert uniq == list(range(uniq[0], uniq[-1] + 1)), (t, uniq)      # consecutive blocks
-        if pl["blocks"] == tiles:
+        if tiles % pl["blocks"] == 0:
             assert all(len(set(ps)) == 1 for ps in by_tile.values())              # no tile is shared
         if pl["lead"]:
             n_left = tiles - pl["blocks"]
