@@ -655,15 +655,14 @@ static int tc_split(int rowsA, int rowsB, int K, int sms) {
 #ifndef TC_SPLIT_OVER
 #define TC_SPLIT_OVER 6
 #endif
-  // Two blocks of the narrowest tiles fit on an SM, so a few more blocks than SMs cost
-  // nothing, and one more cut fills the GPU where tiles * s falls well short of it
-  // (40 tiles: 160 blocks instead of 120 on 148 SMs).
-  // The 32- and 64-column tiles get the extra cut only where they would otherwise not be
-  // cut at all (80 tiles on 148 SMs), and then take the launch with four stages
-  // (TcConfig's LEAN), which is what lets the 160 blocks run in one go.  Where they are
-  // cut anyway (20 tiles seven ways: 140 blocks) the GPU is full enough, and with six
-  // stages one more cut would mean a second wave.
-  if ((bn <= 16 || (bn <= 64 && s == 1)) && TC_SPLIT_OVER > 0 &&
+  // Two blocks of the tiles of up to 64 columns fit on an SM (the 16-column ones with six
+  // stages, the wider ones with the four of TcConfig's LEAN, which a launch with more blocks
+  // than SMs takes), so a few more blocks than SMs cost nothing, and one more cut fills the
+  // GPU where tiles * s falls well short of it (40 tiles: 160 blocks instead of 120 on 148
+  // SMs).  Measured for the wider tiles, decode steps at batch 32 / 64 with and without the
+  // extra cut (ms): 4B sizes 3.857 / 5.826 against 3.871 / 5.842, 8B sizes 5.04 / 7.08 against
+  // 5.11 / 7.12, 32B sizes 15.08 / 19.38 against 15.33 / 19.51.
+  if (bn <= 64 && TC_SPLIT_OVER > 0 &&
       tiles * (s + 1) <= sms + sms / TC_SPLIT_OVER)
     s += 1;
   if (s > kblocks / 4) s = kblocks / 4;
