@@ -176,7 +176,10 @@ struct TcConfig {
       (LEAN && BN <= 64) ? 4
       : BN >= 256 ? 4 : (BN >= 128 ? 6 : (BN >= 64 ? TC_STAGES_64 : (BN >= 32 ? TC_STAGES_32 : TC_STAGES_16)));
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256;
+  // Staging for the fused gate|up epilogue of the 32- and 64-column tiles: [BN tokens][64
+  // features] bf16 (see the epilogue).
+  static constexpr int EPI_BYTES = (BN == 32 || BN == 64) ? BN * 128 : 0;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 + EPI_BYTES;
   // instruction descriptor: f32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
   static constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                     ((uint32_t)(TC_BM >> 4) << 24);
@@ -195,6 +198,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   uint64_t* empty = bars + STAGES;          // [STAGES]
   uint64_t* acc_full = bars + 2 * STAGES;   // [2]
   uint64_t* acc_empty = acc_full + 2;       // [2]
+  uint8_t* epi_s = (uint8_t*)bars + 256;    // [BN][64] bf16, wide tiles with the gate|up epilogue only
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ int last_s;
@@ -458,6 +462,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         write_out = last_s != 0;
         if (write_out) __threadfence();
       }
+      // The gate|up epilogue of a wide tile goes through shared memory: a thread holds one
+      // feature of every token, so straight to memory it stores two bytes at a time, 64
+      // instructions a thread and 32 bytes a warp each; the tile's [tokens][64 features] is
+      // put together in shared memory instead and written as whole 128-byte rows.  (At the
+      // 4B sizes and batch 64 the epilogue of the one tile a block has is not hidden behind
+      // anything: 3.6 of the product's 22 us.)
+      const bool staged = Cfg::EPI_BYTES > 0 && a.transpose_out && a.silu && !a.out_f32 && (a.ld & 7) == 0 &&
+                          (((uintptr_t)a.out) & 15) == 0;
       if (write_out) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -526,6 +538,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 st_f32_if(pf, val, mine && j < valid);
                 pf += ld;
               }
+            } else if (staged) {
+              // feature (r >> 4) * 8 + (r & 7) of token c0 + j (rows and tokens beyond the
+              // product's are left out when the rows are written)
+              const uint32_t sp = smem_u32(epi_s) + (uint32_t)(c0 * 128 + ((r >> 4) * 8 + (r & 7)) * 2);
+              const bool gate_lane = (lane & 15) < 8;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float up = __shfl_down_sync(0xffffffffu, f[j], 8);
+                const float val = __fdividef(f[j], 1.0f + __expf(-f[j])) * up;
+                asm volatile("{ .reg .pred q; setp.ne.b32 q, %2, 0; @q st.shared.b16 [%0], %1; }" ::"r"(sp + j * 128),
+                             "h"(__bfloat16_as_ushort(__float2bfloat16_rn(val))), "r"((int)gate_lane)
+                             : "memory");
+              }
             } else {
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
@@ -587,6 +612,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               }
             }
           }
+        }
+        if (staged) {
+          asm volatile("bar.sync 1, 128;" ::: "memory");   // the tile is complete in shared memory
+          const int feats = a.rowsA >> 1;                  // features of the whole product
+          for (int i = et; i < BN * 8; i += 128) {
+            const int token = i >> 3, col = tb * BN + token, f0 = ta * (TC_BM / 2) + (i & 7) * 8;
+            if (col < a.rowsB && f0 < feats)               // (features come in whole groups of eight)
+              *reinterpret_cast<uint4*>((bf16*)a.out + (size_t)col * a.ld + f0) =
+                  *reinterpret_cast<const uint4*>(epi_s + token * 128 + (i & 7) * 16);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");   // before the next tile is staged
         }
         if (!whole && et == 0) a.counters[tile] = 0u;   // ready for the next launch
       }

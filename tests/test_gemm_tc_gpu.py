@@ -68,8 +68,10 @@ def test_twice_in_a_row_and_row_independence():
     assert torch.equal(a, b)
 
 
-@pytest.mark.parametrize("M", [1, 8, 33, 64])
-@pytest.mark.parametrize("I,K", [(152, 96), (9728, 2560), (24, 4096)])
+@pytest.mark.parametrize("M", [1, 8, 17, 33, 40, 64])
+@pytest.mark.parametrize("I,K", [(152, 96), (9728, 2560), (24, 4096), (1000, 264),
+                                 # 400 tiles: several whole tiles per block at 32 and 64 columns
+                                 (25600, 512)])
 def test_silu_epilogue(M, I, K):
     """Gate and up rows interleaved in groups of 8; the kernel returns silu(gate) * up."""
     from grout_b200.kernels import ops
